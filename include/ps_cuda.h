@@ -26,7 +26,7 @@ extern "C" {
 #define PS_CUDA_ABI_VERSION 1
 
 /* ggml type ids as stored in GGUF (libs/ggml/include/ggml.h:386-401) */
-enum ps_cuda_type { PS_TYPE_F32 = 0, PS_TYPE_Q4_0 = 2, PS_TYPE_Q8_0 = 8, PS_TYPE_Q4_K = 12, PS_TYPE_Q6_K = 14 };
+enum ps_cuda_type { PS_TYPE_F32 = 0, PS_TYPE_Q4_0 = 2, PS_TYPE_Q8_0 = 8, PS_TYPE_Q4_K = 12, PS_TYPE_Q6_K = 14, PS_TYPE_I32 = 26, PS_TYPE_BF16 = 30 };
 
 enum ps_cuda_status {
     PS_CUDA_OK = 0,
@@ -206,6 +206,73 @@ int ps_cuda_tp_init(ps_cuda_ctx *ctx, const void *id128);      /* every rank, af
  * makes them use the fence + epoch-flag protocol as well. */
 int ps_cuda_tp_export(ps_cuda_ctx *ctx, void *handle64);
 int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
+
+/* ---------------------------------------------------------------------------------------------- layer-list models
+ * Models that a configuration file describes layer by layer (config.json + model.safetensors, weights in bfloat16)
+ * instead of the fixed llama / qwen2 stack above.  A layer is a token mixer plus an optional feed-forward, both reading
+ * ONE norm's output ("parallel block"): x <- x + (mixer(N(x)) + ff(N(x))).  Every mechanism is a parameter set of its
+ * own, so that another design can combine them differently:
+ *   attention  - grouped-query, separate query/key and value head sizes, projection biases, no rotation;
+ *                score = q.k * score_scale [* head_temp[h]] [+ rel[bucket(i - j)][h]] [mixed over heads by head_mix],
+ *                soft-max with an optional sink (one more term exp(0) in the denominator that carries no value);
+ *                bucket(n) = n below rel_buckets / 2, then logarithmic up to rel_max_dist (last bucket beyond).
+ *   routed ff  - n_experts gated experts, the top_k largest router scores choose; router_act 1 = sigmoid scores;
+ *                route_on_input = 1: the score multiplies the expert's INPUT; route_renorm = 1: the chosen scores are
+ *                divided by their sum.  Expert: g = min(Wg z, act_limit), u = clamp(Wu z, +-act_limit),
+ *                y = g * sigmoid(act_alpha * g) * (u + up_shift), out = Wd y.
+ *   norm       - RMS norm with eps inside the root; norm_unit_offset = 1: the stored weight is around zero (1 + w).
+ * The context made by ps_cuda_create_arch is an ordinary ps_cuda_ctx: ps_cuda_forward, ps_cuda_decode_greedy,
+ * ps_cuda_sample_topk, ps_cuda_logits_dev, the ps_cuda_kv_* position calls and the ps_cuda_session_* calls work on it
+ * as on a llama context (the per-layer cache rows have the layer's own widths; V is kept transposed like there).  The
+ * llama-only entry points (operator table on the context's workspace, forward_tree, forward_sessions, slot operations,
+ * tensor parallelism) return PS_CUDA_ERR_UNSUPPORTED.
+ * compute = PS_COMPUTE_BF16: matrix products take bfloat16 operands and accumulate in fp32; the residual stream, norms,
+ * attention scores / weights, routers and the cache stay fp32.  PS_COMPUTE_F32: every product in true fp32 (FMA). */
+enum ps_cuda_compute { PS_COMPUTE_BF16 = 0, PS_COMPUTE_F32 = 1 };
+enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1 };
+enum ps_cuda_mlp_kind { PS_MLP_NONE = 0, PS_MLP_ROUTED = 1 };
+
+typedef struct {
+    int32_t mixer_kind;
+    int32_t n_heads, n_kv_heads, qk_dim, v_dim;
+    float   score_scale;
+    int32_t proj_bias;                  /* q, k, v and output projections carry biases */
+    int32_t head_temp;                  /* per-head score multiplier */
+    int32_t rel_buckets; float rel_max_dist; /* rows of the distance-bias table (0 = none) and the distance of its last bucket */
+    int32_t head_mix;                   /* [H][H] mixing of the heads' scores before the soft-max */
+    int32_t sink;                       /* soft-max denominator has one more term of score 0 */
+    int32_t mlp_kind;
+    int32_t n_experts, top_k, expert_ff;
+    int32_t router_act;                 /* 1 = sigmoid */
+    int32_t route_on_input, route_renorm;
+    float   act_limit, act_alpha, up_shift;
+} ps_cuda_layer_desc;
+
+typedef struct {
+    int32_t dim, vocab_size, n_layers;
+    int32_t n_ctx, max_batch;
+    float   norm_eps, embed_scale;
+    int32_t norm_unit_offset;
+    int32_t compute;                    /* enum ps_cuda_compute */
+    const ps_cuda_layer_desc *layers;   /* n_layers entries */
+} ps_cuda_arch_desc;
+
+/* matrices [out][in] in bfloat16; vectors and the small tables in bfloat16 or fp32 */
+typedef struct {
+    ps_cuda_tensor norm, q, q_bias, k, k_bias, v, v_bias, o, o_bias, rel, head_mix, head_temp, router;
+    const ps_cuda_tensor *gate, *up, *down; /* n_experts entries each (NULL without a feed-forward) */
+} ps_cuda_arch_layer_weights;
+
+typedef struct {
+    ps_cuda_tensor embed, final_norm, head;
+    const ps_cuda_arch_layer_weights *layers;
+} ps_cuda_arch_weights;
+
+int ps_cuda_create_arch(ps_cuda_ctx **out, int device, const ps_cuda_arch_desc *desc);
+int ps_cuda_bind_arch(ps_cuda_ctx *ctx, const ps_cuda_arch_weights *w);
+/* debug / bring-up: the residual stream after layer `layer` of the last forward ([bs][dim] fp32; option "arch_taps" = 1
+ * makes forward keep them) */
+int ps_cuda_arch_tap(ps_cuda_ctx *ctx, int layer, float *host, int bs);
 
 /* execution switches (0/1): "graph" = replay the decode step as a captured CUDA graph, "fused" = fused decode
  * kernels instead of one kernel per table op, "pdl" = programmatic dependent launch between the fused kernels.  All

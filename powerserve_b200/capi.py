@@ -43,6 +43,33 @@ class ModelWeights(C.Structure):
     _fields_ = [("token_embd", Tensor), ("output_norm", Tensor), ("output", Tensor), ("layers", C.POINTER(LayerWeights))]
 
 
+class LayerDesc(C.Structure):
+    """ps_cuda_layer_desc: one layer of a layer-list model (include/ps_cuda.h)"""
+    _fields_ = [("mixer_kind", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("qk_dim", C.c_int32), ("v_dim", C.c_int32),
+                ("score_scale", C.c_float), ("proj_bias", C.c_int32), ("head_temp", C.c_int32), ("rel_buckets", C.c_int32), ("rel_max_dist", C.c_float),
+                ("head_mix", C.c_int32), ("sink", C.c_int32), ("mlp_kind", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32),
+                ("expert_ff", C.c_int32), ("router_act", C.c_int32), ("route_on_input", C.c_int32), ("route_renorm", C.c_int32),
+                ("act_limit", C.c_float), ("act_alpha", C.c_float), ("up_shift", C.c_float)]
+
+
+class ArchDesc(C.Structure):
+    _fields_ = [("dim", C.c_int32), ("vocab_size", C.c_int32), ("n_layers", C.c_int32), ("n_ctx", C.c_int32), ("max_batch", C.c_int32),
+                ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("norm_unit_offset", C.c_int32), ("compute", C.c_int32),
+                ("layers", C.POINTER(LayerDesc))]
+
+
+class ArchLayerWeights(C.Structure):
+    _fields_ = [(n, Tensor) for n in ("norm", "q", "q_bias", "k", "k_bias", "v", "v_bias", "o", "o_bias", "rel", "head_mix", "head_temp", "router")] + \
+               [("gate", C.POINTER(Tensor)), ("up", C.POINTER(Tensor)), ("down", C.POINTER(Tensor))]
+
+
+class ArchWeights(C.Structure):
+    _fields_ = [("embed", Tensor), ("final_norm", Tensor), ("head", Tensor), ("layers", C.POINTER(ArchLayerWeights))]
+
+
+COMPUTE_BF16, COMPUTE_F32 = 0, 1
+MIXER_ATTENTION, MLP_NONE, MLP_ROUTED = 1, 0, 1
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -59,6 +86,9 @@ def load_library() -> C.CDLL:
         "ps_cuda_abi_version": (ci, []),
         "ps_cuda_device_count": (ci, []),
         "ps_cuda_create": (ci, [C.POINTER(vp), ci, C.POINTER(ModelDesc)]),
+        "ps_cuda_create_arch": (ci, [C.POINTER(vp), ci, C.POINTER(ArchDesc)]),
+        "ps_cuda_bind_arch": (ci, [vp, C.POINTER(ArchWeights)]),
+        "ps_cuda_arch_tap": (ci, [vp, ci, vp, ci]),
         "ps_cuda_destroy": (None, [vp]),
         "ps_cuda_last_error": (C.c_char_p, [vp]),
         "ps_cuda_sync": (ci, [vp]),
@@ -166,11 +196,13 @@ class CudaBackend:
     """Mirror of `powerserve::ggml::GGMLBackend`'s operator table (src/backend/ggml/ggml.hpp:216-244) over the C ABI.
     Method names, argument meaning and error behaviour follow the reference; tensors are DeviceBuffers."""
 
-    def __init__(self, desc: ModelDesc, device: int = 0):
+    def __init__(self, desc, device: int = 0):
         self.L = load_library()
         self.desc = desc
         h = C.c_void_p()
-        rc = self.L.ps_cuda_create(C.byref(h), device, C.byref(desc))
+        # a layer-list description (ArchDesc) makes a context of the same kind through its own constructor
+        create = self.L.ps_cuda_create_arch if isinstance(desc, ArchDesc) else self.L.ps_cuda_create
+        rc = create(C.byref(h), device, C.byref(desc))
         if rc != 0:
             raise PsCudaError(f"ps_cuda_create failed ({rc}): {self.L.ps_cuda_last_error(None).decode()}")
         self.h = h

@@ -1,0 +1,406 @@
+// ps_arch.cu - executor of layer-list models (include/ps_cuda.h, "layer-list models"): weights, workspace and the sm_100a
+// kernels of the mechanisms a layer description can name.  The context (ps_cuda.cu) owns the stream, the cache sets and the
+// public entry points; this file owns what happens between the token ids and the logits.
+//
+// Precision contract.  The residual stream, norms, attention scores / soft-max weights, router logits and the K / V cache are
+// fp32 in BOTH compute modes.  PS_COMPUTE_BF16 rounds the ACTIVATION operand of every weight product to bfloat16 (weights are
+// bfloat16 already) and accumulates in fp32; PS_COMPUTE_F32 feeds the fp32 activations unrounded and uses FMA chains only.
+#include "ps_arch.h"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+typedef __nv_bfloat16 bf16;
+
+#include "ps_arch_kernels.cuh"
+
+// ====================================================================================================================== host
+struct PsArchLayer {
+    ps_cuda_layer_desc d{};
+    int qd = 0, kd = 0, vd = 0, od = 0; // H * qk_dim, G * qk_dim, G * v_dim, H * v_dim
+    bf16 *wqkv = nullptr, *wo = nullptr, *router = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
+    float *bqkv = nullptr, *bo = nullptr, *norm = nullptr, *rel = nullptr, *mix = nullptr, *temp = nullptr;
+    uint16_t *bucket = nullptr; // distance -> row of the bias table, n_ctx entries
+};
+
+struct PsArch {
+    ps_cuda_arch_desc d{};
+    std::vector<PsArchLayer> L;
+    std::vector<void *> owned;
+    bool bound = false, round = true;
+    bf16 *embed = nullptr, *head = nullptr;
+    float *final_norm = nullptr;
+    // workspace
+    float *x = nullptr, *h = nullptr, *qkv = nullptr, *att = nullptr, *ao = nullptr, *S = nullptr, *logits = nullptr;
+    float *y = nullptr, *slot = nullptr, *sel_w = nullptr, *row_w = nullptr;
+    int *sel_e = nullptr, *row_token = nullptr, *row_slot = nullptr, *tile_e = nullptr, *tile_row0 = nullptr, *tile_end = nullptr, *n_tiles = nullptr;
+    float *part = nullptr; // decode attention partials
+    int64_t ldS = 0;
+    int max_qkv = 0, max_od = 0, max_h = 0, max_top = 0, max_ff = 0, max_e = 0, max_dv = 0;
+    int taps_on = 0;
+    std::vector<float *> taps;
+    int opt_simple = 0; // 1: every batch width takes the tiled kernels (the single-token kernels are skipped; tests compare the two)
+    int n_sm = 148;
+};
+
+namespace {
+
+int afail(std::string &err, int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    err = buf;
+    return code;
+}
+
+#define PA_CK(call)                                                                                                         \
+    do {                                                                                                                    \
+        cudaError_t e_ = (call);                                                                                            \
+        if (e_ != cudaSuccess) return afail(err, PS_CUDA_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+#define PA_LAUNCH()                                                                                                         \
+    do {                                                                                                                    \
+        if (io.n_launch) ++*io.n_launch;                                                                                    \
+        cudaError_t e_ = cudaGetLastError();                                                                                \
+        if (e_ != cudaSuccess) return afail(err, PS_CUDA_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+int aalloc(PsArch *a, void **p, size_t bytes, std::string &err) {
+    if (bytes == 0) bytes = 16;
+    cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) return afail(err, PS_CUDA_ERR_OOM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    a->owned.push_back(*p);
+    return 0;
+}
+
+inline float bf16_bits_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+// a small tensor (vector / table) as fp32 on the host; bfloat16 widens exactly
+int small_to_f32(const ps_cuda_tensor &t, size_t n, std::vector<float> &out, const char *what, std::string &err) {
+    if (!t.host) return afail(err, PS_CUDA_ERR_INVALID, "bind: tensor %s is missing", what);
+    out.resize(n);
+    if (t.type == PS_TYPE_BF16) {
+        const uint16_t *s = static_cast<const uint16_t *>(t.host);
+        for (size_t i = 0; i < n; i++) out[i] = bf16_bits_to_f32(s[i]);
+    } else if (t.type == PS_TYPE_F32) {
+        memcpy(out.data(), t.host, n * 4);
+    } else {
+        return afail(err, PS_CUDA_ERR_UNSUPPORTED, "bind: tensor %s has type %d (bfloat16 or fp32 expected)", what, t.type);
+    }
+    return 0;
+}
+
+int upload_f32(PsArch *a, float **dst, const std::vector<float> &v, std::string &err) {
+    int rc = aalloc(a, (void **)dst, v.size() * 4, err);
+    if (rc) return rc;
+    PA_CK(cudaMemcpy(*dst, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    return 0;
+}
+
+// a bfloat16 matrix, copied into `dst` (device) as it is
+int upload_mat(bf16 *dst, const ps_cuda_tensor &t, size_t n, const char *what, std::string &err) {
+    if (!t.host) return afail(err, PS_CUDA_ERR_INVALID, "bind: matrix %s is missing", what);
+    if (t.type != PS_TYPE_BF16) return afail(err, PS_CUDA_ERR_UNSUPPORTED, "bind: matrix %s has type %d (bfloat16 expected)", what, t.type);
+    PA_CK(cudaMemcpy(dst, t.host, n * 2, cudaMemcpyHostToDevice));
+    return 0;
+}
+
+// distance -> row of a bias table with `rows` rows whose last bucket starts at distance `dmax`: identity below rows / 2, then
+// logarithmic.  Evaluated once on the host in float32, in the order the formula is written.
+void build_bucket_table(int rows, float dmax, int n, std::vector<uint16_t> &t) {
+    t.resize((size_t)n);
+    const int half = rows / 2;
+    const float den = (float)std::log((double)dmax / (double)half);
+    for (int d = 0; d < n; d++) {
+        int b;
+        if (d < half) {
+            b = d;
+        } else {
+            volatile float r = logf((float)d / (float)half);
+            r = r / den;
+            r = r * (float)(rows - half);
+            b = std::min(rows - 1, half + (int)floorf(r));
+        }
+        t[(size_t)d] = (uint16_t)std::max(b, 0);
+    }
+}
+
+// shared memory of the decode attention: q, two score chunks, the mixing matrix, three per-head vectors, the value sums
+size_t pa_decode_smem(int H, int dq, int dv) { return 4 * ((size_t)H * dq + 2 * (size_t)PA_DEC_CHUNK * H + (size_t)H * H + 3 * (size_t)H + (size_t)H * dv); }
+
+} // namespace
+
+int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err) {
+    *out = nullptr;
+    const ps_cuda_arch_desc &d = *desc;
+    if (d.dim <= 0 || d.vocab_size <= 0 || d.n_layers <= 0 || d.n_ctx <= 0 || d.max_batch <= 0 || !d.layers)
+        return afail(err, PS_CUDA_ERR_INVALID, "layer-list descriptor has non-positive fields");
+    if (d.compute != PS_COMPUTE_BF16 && d.compute != PS_COMPUTE_F32) return afail(err, PS_CUDA_ERR_INVALID, "unknown compute mode %d", d.compute);
+    PsArch *a = new PsArch();
+    a->d = d;
+    a->round = d.compute == PS_COMPUTE_BF16;
+    a->L.resize((size_t)d.n_layers);
+    auto bail = [&](int rc) { ps_arch_destroy(a); return rc; };
+    for (int i = 0; i < d.n_layers; i++) {
+        const ps_cuda_layer_desc &l = d.layers[i];
+        PsArchLayer &w = a->L[(size_t)i];
+        w.d = l;
+        if (l.mixer_kind != PS_MIXER_ATTENTION) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
+        if (l.n_heads <= 0 || l.n_kv_heads <= 0 || l.n_heads % l.n_kv_heads || l.qk_dim <= 0 || l.v_dim <= 0 || l.n_heads > PA_MAX_HEADS)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported head geometry (%d / %d heads, sizes %d / %d; at most %d heads)", i, l.n_heads,
+                              l.n_kv_heads, l.qk_dim, l.v_dim, PA_MAX_HEADS));
+        if (l.rel_buckets < 0 || l.rel_buckets > 65535 || (l.rel_buckets > 0 && (l.rel_buckets < 2 || !(l.rel_max_dist > (float)(l.rel_buckets / 2)))))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: distance-bias table of %d rows up to distance %g", i, l.rel_buckets, (double)l.rel_max_dist));
+        if (l.mlp_kind != PS_MLP_NONE && l.mlp_kind != PS_MLP_ROUTED) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown feed-forward kind %d", i, l.mlp_kind));
+        if (l.mlp_kind == PS_MLP_ROUTED && (l.n_experts <= 0 || l.n_experts > PA_MAX_EXPERTS || l.top_k <= 0 || l.top_k > l.n_experts || l.expert_ff <= 0 || l.router_act != 1))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported routed feed-forward (%d experts, top %d, ff %d, router activation %d)", i, l.n_experts,
+                              l.top_k, l.expert_ff, l.router_act));
+        if (pa_decode_smem(l.n_heads, l.qk_dim, l.v_dim) > 200 * 1024)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of sizes %d / %d exceed the decode attention's shared memory", i, l.n_heads, l.qk_dim, l.v_dim));
+        w.qd = l.n_heads * l.qk_dim; w.kd = l.n_kv_heads * l.qk_dim; w.vd = l.n_kv_heads * l.v_dim; w.od = l.n_heads * l.v_dim;
+        a->max_qkv = std::max(a->max_qkv, w.qd + w.kd + w.vd);
+        a->max_od = std::max(a->max_od, w.od);
+        a->max_h = std::max(a->max_h, l.n_heads);
+        a->max_dv = std::max(a->max_dv, l.v_dim);
+        if (l.mlp_kind == PS_MLP_ROUTED) {
+            a->max_top = std::max(a->max_top, l.top_k);
+            a->max_ff = std::max(a->max_ff, l.expert_ff);
+            a->max_e = std::max(a->max_e, l.n_experts);
+        }
+    }
+    a->d.layers = nullptr; // the caller's array need not outlive this call: the copies live in L
+    const int64_t B = d.max_batch, dim = d.dim;
+    a->ldS = ((int64_t)d.n_ctx + 3) & ~(int64_t)3;
+    int rc = 0;
+    auto AL = [&](auto &ptr, size_t bytes) { if (!rc) rc = aalloc(a, (void **)&ptr, bytes, err); };
+    AL(a->x, 4 * dim * B);
+    AL(a->h, 4 * dim * B);
+    AL(a->ao, 4 * dim * B);
+    AL(a->qkv, 4 * (size_t)a->max_qkv * B);
+    AL(a->att, 4 * (size_t)a->max_od * B);
+    AL(a->S, 4 * (size_t)a->max_h * B * a->ldS);
+    AL(a->logits, 4 * (size_t)d.vocab_size * B);
+    const size_t nrow = (size_t)B * std::max(a->max_top, 1);
+    AL(a->y, 4 * nrow * std::max(a->max_ff, 1));
+    AL(a->slot, 4 * nrow * dim);
+    AL(a->sel_w, 4 * nrow);
+    AL(a->sel_e, 4 * nrow);
+    AL(a->row_w, 4 * nrow);
+    AL(a->row_token, 4 * nrow);
+    AL(a->row_slot, 4 * nrow);
+    const size_t ntile = nrow / PA_TM + (size_t)std::max(a->max_e, 1) + 1;
+    AL(a->tile_e, 4 * ntile);
+    AL(a->tile_row0, 4 * ntile);
+    AL(a->tile_end, 4 * ntile);
+    AL(a->n_tiles, 16);
+    AL(a->part, 4 * (size_t)PA_DEC_SPLITS * a->max_h * ((size_t)a->max_dv + 2));
+    if (rc) return bail(rc);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    { int v = 148; if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) a->n_sm = v; }
+    if (cudaFuncSetAttribute(pa_k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+        cudaGetLastError();
+        return bail(afail(err, PS_CUDA_ERR_CUDA, "cudaFuncSetAttribute(decode attention shared memory) failed"));
+    }
+    *out = a;
+    return 0;
+}
+
+void ps_arch_destroy(PsArch *a) {
+    if (!a) return;
+    for (void *p : a->owned) cudaFree(p);
+    delete a;
+}
+
+size_t ps_arch_k_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(size_t)layer].kd * (size_t)a->d.n_ctx; }
+size_t ps_arch_v_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(size_t)layer].vd * (size_t)a->d.n_ctx; }
+float *ps_arch_logits(PsArch *a) { return a->logits; }
+void ps_arch_set_taps(PsArch *a, int on) { a->taps_on = on; }
+const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 0 && (size_t)layer < a->taps.size()) ? a->taps[(size_t)layer] : nullptr; }
+int ps_arch_set_option(PsArch *a, const char *name, int value) {
+    if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
+    if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
+    return 0;
+}
+
+int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream, std::string &err) {
+    (void)stream;
+    if (a->bound) return afail(err, PS_CUDA_ERR_INVALID, "bind: a model is already bound");
+    const ps_cuda_arch_desc &d = a->d;
+    const size_t dim = (size_t)d.dim;
+    int rc;
+    std::vector<float> tmp;
+    auto vec = [&](float **dst, const ps_cuda_tensor &t, size_t n, const char *what, bool unit_offset) -> int {
+        int r = small_to_f32(t, n, tmp, what, err);
+        if (r) return r;
+        if (unit_offset) for (float &v : tmp) v = 1.0f + v;
+        return upload_f32(a, dst, tmp, err);
+    };
+    if ((rc = aalloc(a, (void **)&a->embed, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->embed, wt->embed, dim * d.vocab_size, "embed", err))) return rc;
+    if ((rc = aalloc(a, (void **)&a->head, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->head, wt->head, dim * d.vocab_size, "head", err))) return rc;
+    if ((rc = vec(&a->final_norm, wt->final_norm, dim, "final norm", d.norm_unit_offset != 0))) return rc;
+    a->taps.assign((size_t)d.n_layers, nullptr);
+    for (int i = 0; i < d.n_layers; i++) {
+        PsArchLayer &w = a->L[(size_t)i];
+        const ps_cuda_layer_desc &l = w.d;
+        const ps_cuda_arch_layer_weights &s = wt->layers[i];
+        char nm[64];
+        snprintf(nm, sizeof nm, "layer %d", i);
+        if ((rc = vec(&w.norm, s.norm, dim, nm, d.norm_unit_offset != 0))) return rc;
+        const size_t nq = (size_t)w.qd, nk = (size_t)w.kd, nv = (size_t)w.vd;
+        if ((rc = aalloc(a, (void **)&w.wqkv, 2 * (nq + nk + nv) * dim, err))) return rc;
+        if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
+            (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
+            return rc;
+        if ((rc = aalloc(a, (void **)&w.wo, 2 * dim * (size_t)w.od, err)) || (rc = upload_mat(w.wo, s.o, dim * (size_t)w.od, "o", err))) return rc;
+        if (l.proj_bias) {
+            std::vector<float> b, part;
+            for (auto pr : {std::make_pair(&s.q_bias, nq), std::make_pair(&s.k_bias, nk), std::make_pair(&s.v_bias, nv)}) {
+                if ((rc = small_to_f32(*pr.first, pr.second, part, "projection bias", err))) return rc;
+                b.insert(b.end(), part.begin(), part.end());
+            }
+            if ((rc = upload_f32(a, &w.bqkv, b, err))) return rc;
+            if ((rc = vec(&w.bo, s.o_bias, dim, "output bias", false))) return rc;
+        }
+        if (l.head_temp && (rc = vec(&w.temp, s.head_temp, (size_t)l.n_heads, "head temperatures", false))) return rc;
+        if (l.head_mix && (rc = vec(&w.mix, s.head_mix, (size_t)l.n_heads * l.n_heads, "head mixing matrix", false))) return rc;
+        if (l.rel_buckets > 0) {
+            if ((rc = vec(&w.rel, s.rel, (size_t)l.rel_buckets * l.n_heads, "distance-bias table", false))) return rc;
+            std::vector<uint16_t> t;
+            build_bucket_table(l.rel_buckets, l.rel_max_dist, d.n_ctx, t);
+            if ((rc = aalloc(a, (void **)&w.bucket, t.size() * 2, err))) return rc;
+            PA_CK(cudaMemcpy(w.bucket, t.data(), t.size() * 2, cudaMemcpyHostToDevice));
+        }
+        if (l.mlp_kind == PS_MLP_ROUTED) {
+            const size_t E = (size_t)l.n_experts, ff = (size_t)l.expert_ff;
+            if (!s.gate || !s.up || !s.down) return afail(err, PS_CUDA_ERR_INVALID, "bind: layer %d has no expert tensors", i);
+            if ((rc = aalloc(a, (void **)&w.router, 2 * E * dim, err)) || (rc = upload_mat(w.router, s.router, E * dim, "router", err))) return rc;
+            if ((rc = aalloc(a, (void **)&w.wgate, 2 * E * ff * dim, err)) || (rc = aalloc(a, (void **)&w.wup, 2 * E * ff * dim, err)) ||
+                (rc = aalloc(a, (void **)&w.wdown, 2 * E * ff * dim, err)))
+                return rc;
+            for (size_t e = 0; e < E; e++)
+                if ((rc = upload_mat(w.wgate + e * ff * dim, s.gate[e], ff * dim, "expert gate", err)) ||
+                    (rc = upload_mat(w.wup + e * ff * dim, s.up[e], ff * dim, "expert up", err)) ||
+                    (rc = upload_mat(w.wdown + e * ff * dim, s.down[e], ff * dim, "expert down", err)))
+                    return rc;
+        }
+    }
+    a->bound = true;
+    return 0;
+}
+
+template <bool ROUND>
+static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_head, std::string &err) {
+    const ps_cuda_arch_desc &d = a->d;
+    const int dim = d.dim, B = d.max_batch;
+    const int n_kv = pos0 + bs;
+    cudaStream_t st = io.stream;
+    const dim3 blk(256);
+    auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
+    const bool single = bs == 1 && !a->opt_simple;
+
+    pa_k_embed<<<bs, 128, 0, st>>>(a->x, a->embed, io.tokens_dev, dim, d.embed_scale);
+    PA_LAUNCH();
+    for (int li = 0; li < d.n_layers; li++) {
+        const PsArchLayer &w = a->L[(size_t)li];
+        const ps_cuda_layer_desc &l = w.d;
+        const int H = l.n_heads, G = l.n_kv_heads, dq = l.qk_dim, dv = l.v_dim, nqkv = w.qd + w.kd + w.vd;
+        pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, w.norm, dim, d.norm_eps);
+        PA_LAUNCH();
+        // ---- token mixer: projections -> cache -> scores -> (mix, soft-max) -> P.V -> output projection
+        if (single) {
+            pa_k_matvec<ROUND><<<cdiv(nqkv, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, w.wqkv, w.bqkv, a->qkv, nqkv, dim);
+        } else {
+            pa_k_linear<ROUND><<<dim3(cdiv(nqkv, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wqkv, w.bqkv, a->qkv, nqkv, bs, nqkv, dim);
+        }
+        PA_LAUNCH();
+        pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+        PA_LAUNCH();
+        PaAttn at;
+        at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
+        at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B;
+        if (single) {
+            const int splits = std::min<int>(PA_DEC_SPLITS, (n_kv + PA_DEC_CHUNK - 1) / PA_DEC_CHUNK);
+            const size_t smem = pa_decode_smem(H, dq, dv);
+            pa_k_attn_decode<<<splits, 256, smem, st>>>(at, a->qkv, io.kc[li], io.vct[li], io.pos_dev, a->part, splits);
+            PA_LAUNCH();
+            pa_k_attn_decode_merge<<<H, 128, 0, st>>>(at, a->part, splits, a->att);
+            PA_LAUNCH();
+        } else {
+            pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs);
+            PA_LAUNCH();
+            pa_k_mix_softmax<<<bs, 256, 4 * (size_t)H * H, st>>>(at, a->S, io.pos_dev, bs);
+            PA_LAUNCH();
+            pa_k_pv<<<dim3(cdiv(dv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->S, io.vct[li], a->att, w.od, io.pos_dev, bs);
+            PA_LAUNCH();
+        }
+        if (single) {
+            pa_k_matvec<ROUND><<<cdiv(dim, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->att, w.wo, w.bo, a->ao, dim, w.od);
+        } else {
+            pa_k_linear<ROUND><<<dim3(cdiv(dim, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->att, w.od, w.wo, w.bo, a->ao, dim, bs, dim, w.od);
+        }
+        PA_LAUNCH();
+        // ---- routed feed-forward on the same normed input
+        int top = 0;
+        if (l.mlp_kind == PS_MLP_ROUTED) {
+            top = l.top_k;
+            const int E = l.n_experts, ff = l.expert_ff, n = bs * top;
+            pa_k_router<<<bs, 256, 0, st>>>(a->h, w.router, dim, E, top, l.route_renorm, a->sel_e, a->sel_w);
+            PA_LAUNCH();
+            if (single) {
+                pa_k_expert_up_mv<ROUND><<<dim3(cdiv(ff, PA_MV_ROWS), top), PA_MV_THREADS, 0, st>>>(a->h, a->sel_e, a->sel_w, w.wgate, w.wup, a->y, ff, dim, l.route_on_input,
+                                                                                                    l.act_limit, l.act_alpha, l.up_shift);
+                PA_LAUNCH();
+                pa_k_expert_down_mv<ROUND><<<dim3(cdiv(dim, PA_MV_ROWS), top), PA_MV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, w.wdown, a->slot, dim, ff, l.route_on_input);
+                PA_LAUNCH();
+            } else {
+                const int max_tiles = n / PA_TM + E + 1;
+                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
+                PA_LAUNCH();
+                pa_k_expert_up<ROUND><<<dim3(cdiv(ff, PA_TN), max_tiles), blk, 0, st>>>(a->h, dim, a->row_token, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles,
+                                                                                        w.wgate, w.wup, a->y, ff, dim, l.route_on_input, l.act_limit, l.act_alpha, l.up_shift);
+                PA_LAUNCH();
+                pa_k_expert_down<ROUND><<<dim3(cdiv(dim, PA_TN), max_tiles), blk, 0, st>>>(a->y, ff, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end,
+                                                                                          a->n_tiles, w.wdown, a->slot, top, dim, ff, l.route_on_input);
+                PA_LAUNCH();
+            }
+        }
+        pa_k_combine<<<dim3(cdiv(dim, 256), bs), 256, 0, st>>>(a->x, a->ao, a->slot, top, dim);
+        PA_LAUNCH();
+        if (a->taps_on) {
+            if (!a->taps[(size_t)li]) { int rc = aalloc(a, (void **)&a->taps[(size_t)li], 4 * (size_t)dim * B, err); if (rc) return rc; }
+            PA_CK(cudaMemcpyAsync(a->taps[(size_t)li], a->x, 4 * (size_t)dim * bs, cudaMemcpyDeviceToDevice, st));
+        }
+    }
+    if (lm_head) {
+        pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, a->final_norm, dim, d.norm_eps);
+        PA_LAUNCH();
+        if (single) {
+            pa_k_matvec<ROUND><<<cdiv(d.vocab_size, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, a->head, nullptr, a->logits, d.vocab_size, dim);
+        } else {
+            pa_k_linear<ROUND><<<dim3(cdiv(d.vocab_size, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, a->head, nullptr, a->logits, d.vocab_size, bs, d.vocab_size, dim);
+        }
+        PA_LAUNCH();
+    }
+    return 0;
+}
+
+int ps_arch_forward(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_head, std::string &err) {
+    if (!a->bound) return afail(err, PS_CUDA_ERR_INVALID, "forward: no model bound");
+    if (bs <= 0 || bs > a->d.max_batch || pos0 < 0 || pos0 + bs > a->d.n_ctx) return afail(err, PS_CUDA_ERR_INVALID, "forward: batch %d at position %d does not fit", bs, pos0);
+    return a->round ? forward_t<true>(a, io, bs, pos0, lm_head, err) : forward_t<false>(a, io, bs, pos0, lm_head, err);
+}

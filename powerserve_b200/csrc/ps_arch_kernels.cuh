@@ -1,0 +1,606 @@
+// ps_arch_kernels.cuh - device code of the layer-list model executor (ps_arch.cu).
+//
+// Tiled kernels (any batch width): one 64 x 64 x 16 fp32 tile core shared by the dense projections, the routed experts
+// (rows gathered per expert), the attention scores (B operand = K cache rows) and P.V (B operand = V^T cache rows).
+// Single-token kernels (bs == 1): warp-per-row bfloat16 mat-vecs and a split-key decode attention with a merge step.
+#pragma once
+
+#define PA_TM 64
+#define PA_TN 64
+#define PA_TK 16
+#define PA_LD (PA_TM + 4)
+#define PA_MAX_HEADS 64
+#define PA_MAX_EXPERTS 256
+#define PA_MV_THREADS 256
+#define PA_MV_ROWS 8        // output rows per mat-vec CTA (one warp each)
+#define PA_DEC_SPLITS 64    // at most this many CTAs share the keys of one decode attention
+#define PA_DEC_CHUNK 32     // keys per inner step of the decode attention
+
+struct PaAttn {
+    int H, G, dq, dv;
+    float scale;
+    const float *temp;      // [H] or null
+    const float *rel;       // [rows][H] or null
+    const uint16_t *bucket; // distance -> row, n_bucket entries
+    int n_bucket;
+    const float *mix;       // [H][H] or null
+    int sink;
+    int n_ctx;
+    int64_t ldS;            // row stride of the score rows
+    int B;                  // rows per head in the score buffer (max_batch)
+};
+
+template <bool ROUND> __device__ __forceinline__ float pa_rnd(float v) {
+    if (ROUND) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+__device__ __forceinline__ float pa_ld(const bf16 *p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float pa_ld(const float *p) { return *p; }
+
+// ---------------------------------------------------------------------------------------------------------------- tile core
+// acc[i][j] += sum_k A(ty * 4 + i, k) * B(tx * 4 + j, k) for the CTA's 64 x 64 tile.  Every thread stages 4 k-values of ONE A
+// row and ONE B row per step: `arow` / `brow` point at row (tid >> 2) of the tile (null = outside: zeros).
+template <bool ROUND, typename BT, int NB>
+__device__ __forceinline__ void pa_tile_mm(float (&acc)[NB][4][4], const float *arow, float ascale, const BT *brow0, const BT *brow1, int K, float (*As)[PA_LD],
+                                           float (*Bs)[PA_TK][PA_LD]) {
+    const int tid = threadIdx.x, lr = tid >> 2, kq = (tid & 3) * 4, tx = tid & 15, ty = tid >> 4;
+    for (int k0 = 0; k0 < K; k0 += PA_TK) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int kk = k0 + kq + c;
+            const bool in = kk < K;
+            As[kq + c][lr] = (arow && in) ? pa_rnd<ROUND>(arow[kk] * ascale) : 0.f;
+            Bs[0][kq + c][lr] = (brow0 && in) ? pa_ld(brow0 + kk) : 0.f;
+            if (NB == 2) Bs[NB - 1][kq + c][lr] = (brow1 && in) ? pa_ld(brow1 + kk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < PA_TK; k++) {
+            const float4 a4 = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) {
+                const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[nb][k][tx * 4]);
+                const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[nb][i][j] = fmaf(av[i], bv[j], acc[nb][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+#define PA_TILE_SMEM(NB)                          \
+    __shared__ __align__(16) float As[PA_TK][PA_LD]; \
+    __shared__ __align__(16) float Bs[NB][PA_TK][PA_LD]
+
+// ---------------------------------------------------------------------------------------------------------------- small ops
+__global__ void __launch_bounds__(128) pa_k_embed(float *__restrict__ x, const bf16 *__restrict__ table, const int32_t *__restrict__ tokens, int dim, float scale) {
+    const int t = blockIdx.x;
+    const bf16 *row = table + (int64_t)tokens[t] * dim;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) x[(int64_t)t * dim + c] = __bfloat162float(row[c]) * scale;
+}
+
+// h = x / sqrt(mean(x^2) + eps) * w   (w already holds 1 + weight for unit-offset norms)
+__global__ void __launch_bounds__(256) pa_k_norm(float *__restrict__ h, const float *__restrict__ x, const float *__restrict__ w, int dim, float eps) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const float *xr = x + (int64_t)blockIdx.x * dim;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < dim; c += 256) s = fmaf(xr[c], xr[c], s);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; i++) t += red[i];
+        inv_s = 1.0f / sqrtf(t / (float)dim + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int c = threadIdx.x; c < dim; c += 256) h[(int64_t)blockIdx.x * dim + c] = xr[c] * inv * w[c];
+}
+
+// the batch's K rows go to kc[pos][:], its V rows transposed to vct[:][pos]
+__global__ void __launch_bounds__(256) pa_k_kv_store(const float *__restrict__ qkv, int ld, int qd, int kd, int vd, float *__restrict__ kc, float *__restrict__ vct, int n_ctx,
+                                                     const int32_t *__restrict__ pos) {
+    const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    const int p = pos[t];
+    const float *row = qkv + (int64_t)t * ld + qd;
+    if (c < kd) kc[(int64_t)p * kd + c] = row[c];
+    else if (c < kd + vd) vct[(int64_t)(c - kd) * n_ctx + p] = row[c];
+}
+
+// x += mixer + sum of the feed-forward slots (fixed order)
+__global__ void __launch_bounds__(256) pa_k_combine(float *__restrict__ x, const float *__restrict__ ao, const float *__restrict__ slot, int top, int dim) {
+    const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= dim) return;
+    float y = ao[(int64_t)t * dim + c];
+    for (int r = 0; r < top; r++) y += slot[((int64_t)t * top + r) * dim + c];
+    x[(int64_t)t * dim + c] += y;
+}
+
+// ---------------------------------------------------------------------------------------------------------------- dense
+// C[m][n] = sum_k A[m][k] W[n][k] + bias[n]
+template <bool ROUND>
+__global__ void __launch_bounds__(256) pa_k_linear(const float *__restrict__ A, int lda, const bf16 *__restrict__ W, const float *__restrict__ bias, float *__restrict__ C, int ldc,
+                                                   int M, int N, int K) {
+    PA_TILE_SMEM(1);
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    float acc[1][4][4] = {};
+    const float *arow = (m0 + lr < M) ? A + (int64_t)(m0 + lr) * lda : nullptr;
+    const bf16 *brow = (n0 + lr < N) ? W + (int64_t)(n0 + lr) * K : nullptr;
+    pa_tile_mm<ROUND, bf16, 1>(acc, arow, 1.0f, brow, nullptr, K, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(int64_t)m * ldc + n] = acc[0][i][j] + (bias ? bias[n] : 0.f);
+        }
+    }
+}
+
+// one warp per output row, bs == 1: y[n] = sum_k x[k] W[n][k] + bias[n]
+template <bool ROUND> __device__ __forceinline__ float pa_row_dot(const bf16 *__restrict__ wrow, const float *__restrict__ xs, int K, int lane) {
+    float s = 0.f;
+    if ((K & 7) == 0) {
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(wrow + k);
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                s = fmaf(__uint_as_float(u[t] << 16), xs[k + 2 * t], s);
+                s = fmaf(__uint_as_float(u[t] & 0xffff0000u), xs[k + 2 * t + 1], s);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) s = fmaf(__bfloat162float(wrow[k]), xs[k], s);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return s;
+}
+
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_matvec(const float *__restrict__ x, const bf16 *__restrict__ W, const float *__restrict__ bias, float *__restrict__ y, int N, int K) {
+    __shared__ float xs_static[2048];
+    float *xs = K <= 2048 ? xs_static : nullptr;
+    const int lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
+    if (xs) {
+        for (int k = threadIdx.x; k < K; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(x[k]);
+        __syncthreads();
+    }
+    if (n >= N) return;
+    float s;
+    if (xs) {
+        s = pa_row_dot<ROUND>(W + (int64_t)n * K, xs, K, lane);
+    } else { // wide inputs: read (and round) the activation from global memory
+        s = 0.f;
+        const bf16 *wrow = W + (int64_t)n * K;
+        for (int k = lane; k < K; k += 32) s = fmaf(__bfloat162float(wrow[k]), pa_rnd<ROUND>(x[k]), s);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    }
+    if (lane == 0) y[n] = s + (bias ? bias[n] : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------------------------- router
+// scores = sigmoid(W_r h) in fp32; the top_k largest (ties: the lower expert) -> sel_e / sel_w [token][top_k]
+__global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, const bf16 *__restrict__ Wr, int dim, int E, int top, int renorm, int *__restrict__ sel_e,
+                                                   float *__restrict__ sel_w) {
+    __shared__ float sc[PA_MAX_EXPERTS];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *hr = h + (int64_t)t * dim;
+    for (int e = warp; e < E; e += 8) {
+        const bf16 *wr = Wr + (int64_t)e * dim;
+        float s = 0.f;
+        for (int k = lane; k < dim; k += 32) s = fmaf(__bfloat162float(wr[k]), hr[k], s);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-s));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.f;
+        for (int r = 0; r < top; r++) {
+            int best = 0;
+            float bv = -1.f;
+            for (int e = 0; e < E; e++)
+                if (sc[e] > bv) { bv = sc[e]; best = e; }
+            sel_e[t * top + r] = best;
+            sel_w[t * top + r] = bv;
+            sum += bv;
+            sc[best] = -2.f;
+        }
+        if (renorm)
+            for (int r = 0; r < top; r++) sel_w[t * top + r] /= sum;
+    }
+}
+
+// (token, slot) pairs grouped by expert: row lists + the table of 64-row tiles the expert kernels walk
+__global__ void __launch_bounds__(256) pa_k_dispatch(const int *__restrict__ sel_e, const float *__restrict__ sel_w, int n, int top, int E, int *__restrict__ row_token,
+                                                     int *__restrict__ row_slot, float *__restrict__ row_w, int *__restrict__ tile_e, int *__restrict__ tile_row0,
+                                                     int *__restrict__ tile_end, int *__restrict__ n_tiles) {
+    __shared__ int cnt[PA_MAX_EXPERTS], off[PA_MAX_EXPERTS], fill[PA_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < E; e += 256) { cnt[e] = 0; fill[e] = 0; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += 256) atomicAdd(&cnt[sel_e[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            off[e] = o;
+            for (int r = 0; r < cnt[e]; r += PA_TM) { tile_e[nt] = e; tile_row0[nt] = o + r; tile_end[nt] = o + cnt[e]; nt++; }
+            o += cnt[e];
+        }
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const int e = sel_e[i];
+        const int p = off[e] + atomicAdd(&fill[e], 1);
+        row_token[p] = i / top;
+        row_slot[p] = i % top;
+        row_w[p] = sel_w[i];
+    }
+}
+
+__device__ __forceinline__ float pa_expert_act(float g, float u, float limit, float alpha, float shift) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
+}
+
+// y[r][n] = act(gate_e . z_r, up_e . z_r), z_r = w_r * h[token_r] (route_on_input) or h[token_r]
+template <bool ROUND>
+__global__ void __launch_bounds__(256) pa_k_expert_up(const float *__restrict__ h, int ldh, const int *__restrict__ row_token, const float *__restrict__ row_w,
+                                                      const int *__restrict__ tile_e, const int *__restrict__ tile_row0, const int *__restrict__ tile_end,
+                                                      const int *__restrict__ n_tiles, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int ff,
+                                                      int dim, int on_input, float limit, float alpha, float shift) {
+    PA_TILE_SMEM(2);
+    if ((int)blockIdx.y >= *n_tiles) return;
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int e = tile_e[blockIdx.y], r0 = tile_row0[blockIdx.y], rend = tile_end[blockIdx.y], n0 = blockIdx.x * PA_TN;
+    float acc[2][4][4] = {};
+    const bool rin = r0 + lr < rend;
+    const float *arow = rin ? h + (int64_t)row_token[r0 + lr] * ldh : nullptr;
+    const float ascale = (rin && on_input) ? row_w[r0 + lr] : 1.0f;
+    const int64_t wofs = ((int64_t)e * ff + n0 + lr) * dim;
+    const bool nin = n0 + lr < ff;
+    pa_tile_mm<ROUND, bf16, 2>(acc, arow, ascale, nin ? Wg + wofs : nullptr, nin ? Wu + wofs : nullptr, dim, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = r0 + ty * 4 + i;
+        if (r >= rend) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < ff) y[(int64_t)r * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], limit, alpha, shift);
+        }
+    }
+}
+
+// slot[token_r][slot_r][n] = down_e . y_r  (times w_r when the score weighs the OUTPUT)
+template <bool ROUND>
+__global__ void __launch_bounds__(256) pa_k_expert_down(const float *__restrict__ y, int ff_ld, const int *__restrict__ row_token, const int *__restrict__ row_slot,
+                                                        const float *__restrict__ row_w, const int *__restrict__ tile_e, const int *__restrict__ tile_row0,
+                                                        const int *__restrict__ tile_end, const int *__restrict__ n_tiles, const bf16 *__restrict__ Wd, float *__restrict__ slot,
+                                                        int top, int dim, int ff, int on_input) {
+    PA_TILE_SMEM(1);
+    if ((int)blockIdx.y >= *n_tiles) return;
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int e = tile_e[blockIdx.y], r0 = tile_row0[blockIdx.y], rend = tile_end[blockIdx.y], n0 = blockIdx.x * PA_TN;
+    float acc[1][4][4] = {};
+    const float *arow = (r0 + lr < rend) ? y + (int64_t)(r0 + lr) * ff_ld : nullptr;
+    const bf16 *brow = (n0 + lr < dim) ? Wd + ((int64_t)e * dim + n0 + lr) * ff : nullptr;
+    pa_tile_mm<ROUND, bf16, 1>(acc, arow, 1.0f, brow, nullptr, ff, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = r0 + ty * 4 + i;
+        if (r >= rend) continue;
+        const float w = on_input ? 1.0f : row_w[r];
+        float *dst = slot + ((int64_t)row_token[r] * top + row_slot[r]) * dim;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < dim) dst[n] = acc[0][i][j] * w;
+        }
+    }
+}
+
+// single token: grid (row blocks, top_k); expert ids come from device memory
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_expert_up_mv(const float *__restrict__ h, const int *__restrict__ sel_e, const float *__restrict__ sel_w,
+                                                                   const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, int on_input,
+                                                                   float limit, float alpha, float shift) {
+    __shared__ float xs[2048];
+    const int r = blockIdx.y, e = sel_e[r], lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
+    const float w = on_input ? sel_w[r] : 1.0f;
+    const bool staged = dim <= 2048;
+    if (staged) {
+        for (int k = threadIdx.x; k < dim; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(h[k] * w);
+        __syncthreads();
+    }
+    if (n >= ff) return;
+    const bf16 *gr = Wg + ((int64_t)e * ff + n) * dim, *ur = Wu + ((int64_t)e * ff + n) * dim;
+    float g, u;
+    if (staged) {
+        g = pa_row_dot<ROUND>(gr, xs, dim, lane);
+        u = pa_row_dot<ROUND>(ur, xs, dim, lane);
+    } else {
+        g = u = 0.f;
+        for (int k = lane; k < dim; k += 32) {
+            const float z = pa_rnd<ROUND>(h[k] * w);
+            g = fmaf(__bfloat162float(gr[k]), z, g);
+            u = fmaf(__bfloat162float(ur[k]), z, u);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) { g += __shfl_xor_sync(0xffffffffu, g, o); u += __shfl_xor_sync(0xffffffffu, u, o); }
+    }
+    if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(g, u, limit, alpha, shift);
+}
+
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_expert_down_mv(const float *__restrict__ y, const int *__restrict__ sel_e, const float *__restrict__ sel_w,
+                                                                     const bf16 *__restrict__ Wd, float *__restrict__ slot, int dim, int ff, int on_input) {
+    __shared__ float xs[2048];
+    const int r = blockIdx.y, e = sel_e[r], lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
+    const float *yr = y + (int64_t)r * ff;
+    const bool staged = ff <= 2048;
+    if (staged) {
+        for (int k = threadIdx.x; k < ff; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(yr[k]);
+        __syncthreads();
+    }
+    if (n >= dim) return;
+    const bf16 *dr = Wd + ((int64_t)e * dim + n) * ff;
+    float s;
+    if (staged) {
+        s = pa_row_dot<ROUND>(dr, xs, ff, lane);
+    } else {
+        s = 0.f;
+        for (int k = lane; k < ff; k += 32) s = fmaf(__bfloat162float(dr[k]), pa_rnd<ROUND>(yr[k]), s);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    }
+    if (lane == 0) slot[(int64_t)r * dim + n] = s * (on_input ? 1.0f : sel_w[r]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------- attention
+__device__ __forceinline__ float pa_score(const PaAttn &at, float dot, int h, int dist) {
+    float s = dot * at.scale;
+    if (at.temp) s *= at.temp[h];
+    if (at.rel) s += at.rel[(int)at.bucket[min(dist, at.n_bucket - 1)] * at.H + h];
+    return s;
+}
+
+// S[h][i][j] = score of query i (position pos[i]) and cache row j <= pos[i], before the heads are mixed
+__global__ void __launch_bounds__(256) pa_k_scores(PaAttn at, const float *__restrict__ qkv, int ldq, const float *__restrict__ kc, int kd, float *__restrict__ S,
+                                                   const int32_t *__restrict__ pos, int bs) {
+    PA_TILE_SMEM(1);
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    const int pos0 = pos[0], last = pos0 + min(m0 + PA_TM, bs) - 1; // the tile's furthest query
+    if (n0 > last) return;
+    float acc[1][4][4] = {};
+    const float *arow = (m0 + lr < bs) ? qkv + (int64_t)(m0 + lr) * ldq + h * at.dq : nullptr;
+    const float *brow = (n0 + lr <= last) ? kc + (int64_t)(n0 + lr) * kd + g * at.dq : nullptr;
+    pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, at.dq, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= bs) continue;
+        const int p = pos0 + m;
+        float *row = S + ((int64_t)h * at.B + m) * at.ldS;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n <= p) row[n] = pa_score(at, acc[0][i][j], h, p - n);
+        }
+    }
+}
+
+// per query: mix the heads' scores (b_h = sum_g T[h][g] a_g), soft-max every head's row (optionally with a sink term in the
+// denominator), zero the row's tail up to the end of the batch so that P.V can run whole tiles
+template <int MAXH>
+__device__ __forceinline__ void pa_mix_rows(const PaAttn &at, float *S, int i, int n, const float *Ts) {
+    const int H = at.H;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float a[MAXH];
+#pragma unroll
+        for (int g = 0; g < MAXH; g++) a[g] = g < H ? S[((int64_t)g * at.B + i) * at.ldS + j] : 0.f;
+        for (int h = 0; h < H; h++) {
+            float s = 0.f;
+#pragma unroll
+            for (int g = 0; g < MAXH; g++)
+                if (g < H) s = fmaf(Ts[h * H + g], a[g], s);
+            S[((int64_t)h * at.B + i) * at.ldS + j] = s;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) pa_k_mix_softmax(PaAttn at, float *__restrict__ S, const int32_t *__restrict__ pos, int bs) {
+    extern __shared__ float Ts[];
+    const int i = blockIdx.x, H = at.H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = pos[i] + 1, n_end = pos[0] + bs;
+    if (at.mix) {
+        for (int t = threadIdx.x; t < H * H; t += 256) Ts[t] = at.mix[t];
+        __syncthreads();
+        if (H <= 8) pa_mix_rows<8>(at, S, i, n, Ts);
+        else if (H <= 16) pa_mix_rows<16>(at, S, i, n, Ts);
+        else if (H <= 32) pa_mix_rows<32>(at, S, i, n, Ts);
+        else pa_mix_rows<PA_MAX_HEADS>(at, S, i, n, Ts);
+        __syncthreads();
+    }
+    for (int h = warp; h < H; h += 8) {
+        float *row = S + ((int64_t)h * at.B + i) * at.ldS;
+        float mx = at.sink ? 0.f : -INFINITY;
+        for (int j = lane; j < n; j += 32) mx = fmaxf(mx, row[j]);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int j = lane; j < n; j += 32) {
+            const float e = expf(row[j] - mx);
+            row[j] = e;
+            sum += e;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (at.sink) sum += expf(-mx);
+        const float inv = 1.0f / sum;
+        for (int j = lane; j < n; j += 32) row[j] *= inv;
+        for (int j = n + lane; j < n_end; j += 32) row[j] = 0.f;
+    }
+}
+
+// att[i][h * dv + c] = sum_j P[h][i][j] V^T[g * dv + c][j]
+__global__ void __launch_bounds__(256) pa_k_pv(PaAttn at, const float *__restrict__ S, const float *__restrict__ vct, float *__restrict__ att, int od,
+                                               const int32_t *__restrict__ pos, int bs) {
+    PA_TILE_SMEM(1);
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    const int n_keys = pos[0] + min(m0 + PA_TM, bs); // keys the tile's furthest query sees (the rows are zero beyond their own)
+    float acc[1][4][4] = {};
+    const float *arow = (m0 + lr < bs) ? S + ((int64_t)h * at.B + m0 + lr) * at.ldS : nullptr;
+    const float *brow = (n0 + lr < at.dv) ? vct + (int64_t)(g * at.dv + n0 + lr) * at.n_ctx : nullptr;
+    pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, n_keys, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= bs) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < at.dv) att[(int64_t)m * od + h * at.dv + n] = acc[0][i][j];
+        }
+    }
+}
+
+// ---- single token: the keys are split over the CTAs; each keeps a running (max, sum, weighted values) per head over chunks of
+// PA_DEC_CHUNK keys - scores of ALL heads for a chunk, mixing, online soft-max, P.V - and leaves its partial for the merge.
+// part[(split * H + h) * (dv + 2)] = {m, l, acc[dv]}
+__global__ void __launch_bounds__(256) pa_k_attn_decode(PaAttn at, const float *__restrict__ qkv, const float *__restrict__ kc, const float *__restrict__ vct,
+                                                        const int32_t *__restrict__ pos_dev, float *__restrict__ part, int splits) {
+    extern __shared__ float sm[];
+    const int H = at.H, G = at.G, dq = at.dq, dv = at.dv, rep = H / G, kd = G * dq;
+    float *qs = sm;                          // [H][dq]
+    float *sa = qs + H * dq;                 // [CHUNK][H] raw scores
+    float *sb = sa + PA_DEC_CHUNK * H;       // [CHUNK][H] mixed scores -> weights
+    float *Ts = sb + PA_DEC_CHUNK * H;       // [H][H]
+    float *ms = Ts + H * H;                  // [H] running max
+    float *ls = ms + H;                      // [H] running sum
+    float *al = ls + H;                      // [H] rescale factor of the step
+    float *acc = al + H;                     // [H][dv]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pos = pos_dev[0], n = pos + 1;
+    const int per = (n + splits - 1) / splits, j_lo = blockIdx.x * per, j_hi = min(n, j_lo + per);
+    for (int t = tid; t < H * dq; t += 256) qs[t] = qkv[t];
+    if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t];
+    for (int t = tid; t < H; t += 256) { ms[t] = at.sink ? 0.f : -INFINITY; ls[t] = 0.f; }
+    for (int t = tid; t < H * dv; t += 256) acc[t] = 0.f;
+    __syncthreads();
+    for (int j0 = j_lo; j0 < j_hi; j0 += PA_DEC_CHUNK) {
+        const int nj = min(PA_DEC_CHUNK, j_hi - j0);
+        // raw scores: one warp per key, lanes over the key row; every query head of a kv group reuses the loaded value
+        for (int jj = warp; jj < nj; jj += 8) {
+            const float *krow = kc + (int64_t)(j0 + jj) * kd;
+            for (int g = 0; g < G; g++) {
+                for (int r0 = 0; r0 < rep; r0 += 4) {
+                    float s[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int d = lane; d < dq; d += 32) {
+                        const float kv = krow[g * dq + d];
+#pragma unroll
+                        for (int r = 0; r < 4; r++)
+                            if (r0 + r < rep) s[r] = fmaf(kv, qs[(g * rep + r0 + r) * dq + d], s[r]);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        if (r0 + r >= rep) break;
+#pragma unroll
+                        for (int o = 16; o; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+                    }
+                    if (lane == 0) {
+#pragma unroll
+                        for (int r = 0; r < 4; r++)
+                            if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = pa_score(at, s[r], g * rep + r0 + r, pos - (j0 + jj));
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // mix the heads
+        for (int t = tid; t < nj * H; t += 256) {
+            const int jj = t / H, h = t % H;
+            float s;
+            if (at.mix) {
+                s = 0.f;
+                for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
+            } else {
+                s = sa[t];
+            }
+            sb[t] = s;
+        }
+        __syncthreads();
+        // online soft-max bookkeeping: one warp per head
+        for (int h = warp; h < H; h += 8) {
+            float mx = -INFINITY;
+            for (int jj = lane; jj < nj; jj += 32) mx = fmaxf(mx, sb[jj * H + h]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_old = ms[h], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int jj = lane; jj < nj; jj += 32) {
+                const float e = expf(sb[jj * H + h] - m_new);
+                sb[jj * H + h] = e;
+                sum += e;
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                const float a = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+                al[h] = a;
+                ls[h] = ls[h] * a + sum;
+                ms[h] = m_new;
+            }
+        }
+        __syncthreads();
+        // weighted values: one thread per (head, value dim), contiguous along the keys of V^T
+        for (int o = tid; o < H * dv; o += 256) {
+            const int h = o / dv, c = o % dv, g = h / rep;
+            const float *vrow = vct + (int64_t)(g * dv + c) * at.n_ctx + j0;
+            float s = acc[o] * al[h];
+            for (int jj = 0; jj < nj; jj++) s = fmaf(sb[jj * H + h], vrow[jj], s);
+            acc[o] = s;
+        }
+        __syncthreads();
+    }
+    float *out = part + (int64_t)blockIdx.x * H * (dv + 2);
+    for (int t = tid; t < H; t += 256) { out[t * (dv + 2)] = ms[t]; out[t * (dv + 2) + 1] = ls[t]; }
+    for (int o = tid; o < H * dv; o += 256) out[(o / dv) * (dv + 2) + 2 + o % dv] = acc[o];
+}
+
+__global__ void __launch_bounds__(128) pa_k_attn_decode_merge(PaAttn at, const float *__restrict__ part, int splits, float *__restrict__ att) {
+    const int h = blockIdx.x, H = at.H, dv = at.dv;
+    float M = at.sink ? 0.f : -INFINITY;
+    for (int s = 0; s < splits; s++) M = fmaxf(M, part[((int64_t)s * H + h) * (dv + 2)]);
+    float Lsum = at.sink ? expf(-M) : 0.f;
+    for (int s = 0; s < splits; s++) {
+        const float *p = part + ((int64_t)s * H + h) * (dv + 2);
+        if (p[0] != -INFINITY) Lsum += p[1] * expf(p[0] - M);
+    }
+    const float inv = 1.0f / Lsum;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) {
+            const float *p = part + ((int64_t)s * H + h) * (dv + 2);
+            if (p[0] != -INFINITY) v = fmaf(p[2 + c], expf(p[0] - M), v);
+        }
+        att[h * dv + c] = v * inv;
+    }
+}

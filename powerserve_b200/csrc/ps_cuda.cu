@@ -6,6 +6,7 @@
 #include "ps_mv32.cuh"
 #include "ps_tc.cuh"
 #include "ps_step.cuh"
+#include "ps_arch.h"
 
 #include <dlfcn.h>
 
@@ -199,6 +200,10 @@ struct ps_cuda_ctx {
     int64_t n_launch = 0, n_graph = 0, h2d = 0, d2h = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr; // device timing of the last forward / decode call (stream events)
     double last_ms = 0.0;
+    // layer-list model (ps_cuda_create_arch): weights, workspace and kernels live in the executor (ps_arch.cu); the context keeps
+    // what every model family shares - stream, staging, cache sets / sessions, positions, logits read-back, sampling
+    PsArch *arch = nullptr;
+    std::vector<size_t> kv_k_bytes, kv_v_bytes; // per layer: bytes of the K rows / V^T rows of ONE cache set
 };
 
 namespace {
@@ -227,6 +232,12 @@ int fail(ps_cuda_ctx *c, int code, const char *fmt, ...) {
         cudaError_t e_ = cudaGetLastError();                                                                 \
         if (e_ != cudaSuccess)                                                                               \
             return fail(ctx, PS_CUDA_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+// entry points that work on the llama-family workspace / cache layout only
+#define PS_NO_ARCH(what)                                                                                    \
+    do {                                                                                                    \
+        if (ctx->arch) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, what ": not available on a layer-list context"); \
     } while (0)
 
 int dev_alloc(ps_cuda_ctx *ctx, void **p, size_t bytes) {
@@ -1272,6 +1283,87 @@ int ps_cuda_create(ps_cuda_ctx **out, int device, const ps_cuda_model_desc *desc
     return 0;
 }
 
+// A context for a layer-list model: the same object as a llama context minus the llama workspace.  What the shared entry
+// points read from `d` (vocabulary, layers, cache length, batch cap) is filled in; the per-layer cache rows take the widths
+// the executor reports.
+int ps_cuda_create_arch(ps_cuda_ctx **out, int device, const ps_cuda_arch_desc *desc) {
+    if (!out || !desc) return fail(nullptr, PS_CUDA_ERR_INVALID, "null argument");
+    *out = nullptr;
+    const int ndev = ps_cuda_device_count();
+    if (ndev == 0) return fail(nullptr, PS_CUDA_ERR_NO_DEVICE, "no CUDA device: the PowerServe CUDA backend has no CPU fallback");
+    if (device < 0 || device >= ndev) return fail(nullptr, PS_CUDA_ERR_INVALID, "device %d out of range [0,%d)", device, ndev);
+    if (cudaSetDevice(device) != cudaSuccess) return fail(nullptr, PS_CUDA_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    PsArch *arch = nullptr;
+    std::string err;
+    int rc = ps_arch_create(&arch, desc, err);
+    if (rc) return fail(nullptr, rc, "%s", err.c_str());
+    ps_cuda_ctx *ctx = new ps_cuda_ctx();
+    ctx->device = device;
+    ctx->arch = arch;
+    ctx->d.dim = desc->dim; ctx->d.vocab_size = desc->vocab_size; ctx->d.n_layers = desc->n_layers; ctx->d.n_ctx = desc->n_ctx; ctx->d.max_batch = desc->max_batch;
+    ctx->d.norm_eps = desc->norm_eps; ctx->d.tp_size = 1;
+    auto bail = [&](int code) {
+        g_create_error = ctx->err;
+        ps_cuda_destroy(ctx);
+        return code;
+    };
+    auto ck = [&](cudaError_t e, const char *what) { return e == cudaSuccess ? 0 : fail(ctx, PS_CUDA_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e)); };
+    const int64_t B = desc->max_batch;
+    if ((rc = ck(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate"))) return bail(rc);
+    if ((rc = dev_alloc(ctx, (void **)&ctx->tokens_dev, 4 * B)) || (rc = dev_alloc(ctx, (void **)&ctx->pos_dev, 4 * B)) || (rc = dev_alloc(ctx, (void **)&ctx->ids_dev, 4 * 4096)) ||
+        (rc = dev_alloc(ctx, (void **)&ctx->ctr_dev, 16)) || (rc = dev_alloc(ctx, (void **)&ctx->err_dev, 128)))
+        return bail(rc);
+    if ((rc = ck(cudaMemsetAsync(ctx->err_dev, 0, 128, ctx->stream), "cudaMemsetAsync"))) return bail(rc);
+    ctx->tc_err_dev = ctx->err_dev;
+    ctx->tp_err_dev = ctx->err_dev + 1;
+    if ((rc = ck(cudaMallocHost(&ctx->h_err, 16), "cudaMallocHost")) || (rc = ck(cudaMallocHost(&ctx->h_tokens, 4 * B), "cudaMallocHost")) ||
+        (rc = ck(cudaMallocHost(&ctx->h_pos, 4 * B), "cudaMallocHost")) || (rc = ck(cudaMallocHost(&ctx->h_ids, 4 * 8192), "cudaMallocHost")))
+        return bail(rc);
+    { int v = 148; if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) ctx->n_sm = v; }
+    ctx->kc.resize(desc->n_layers);
+    ctx->vct.resize(desc->n_layers);
+    ctx->kv_k_bytes.resize(desc->n_layers);
+    ctx->kv_v_bytes.resize(desc->n_layers);
+    for (int L = 0; L < desc->n_layers; L++) {
+        ctx->kv_k_bytes[L] = ps_arch_k_bytes(arch, L);
+        ctx->kv_v_bytes[L] = ps_arch_v_bytes(arch, L);
+        if ((rc = dev_alloc(ctx, (void **)&ctx->kc[L], ctx->kv_k_bytes[L])) || (rc = dev_alloc(ctx, (void **)&ctx->vct[L], ctx->kv_v_bytes[L]))) return bail(rc);
+        if ((rc = ck(cudaMemsetAsync(ctx->kc[L], 0, ctx->kv_k_bytes[L], ctx->stream), "cudaMemsetAsync")) ||
+            (rc = ck(cudaMemsetAsync(ctx->vct[L], 0, ctx->kv_v_bytes[L], ctx->stream), "cudaMemsetAsync")))
+            return bail(rc);
+    }
+    ctx->slot_mask.assign((size_t)desc->n_ctx, 1);
+    ctx->logits = ps_arch_logits(arch);
+    if ((rc = ck(cudaEventCreate(&ctx->ev0), "cudaEventCreate")) || (rc = ck(cudaEventCreate(&ctx->ev1), "cudaEventCreate")) ||
+        (rc = ck(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")))
+        return bail(rc);
+    *out = ctx;
+    return 0;
+}
+
+int ps_cuda_bind_arch(ps_cuda_ctx *ctx, const ps_cuda_arch_weights *w) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (!ctx->arch) return fail(ctx, PS_CUDA_ERR_INVALID, "bind_arch: not a layer-list context");
+    if (!w || !w->layers) return fail(ctx, PS_CUDA_ERR_INVALID, "bind_arch: null argument");
+    PS_CK(cudaSetDevice(ctx->device));
+    std::string err;
+    const int rc = ps_arch_bind(ctx->arch, w, ctx->stream, err);
+    if (rc) return fail(ctx, rc, "%s", err.c_str());
+    ctx->bound = true;
+    return 0;
+}
+
+int ps_cuda_arch_tap(ps_cuda_ctx *ctx, int layer, float *host, int bs) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (!ctx->arch) return fail(ctx, PS_CUDA_ERR_INVALID, "arch_tap: not a layer-list context");
+    const float *src = ps_arch_tap(ctx->arch, layer);
+    if (!src || !host || bs <= 0 || bs > ctx->d.max_batch) return fail(ctx, PS_CUDA_ERR_INVALID, "arch_tap: no tap of layer %d (option arch_taps) or bad size", layer);
+    PS_CK(cudaSetDevice(ctx->device));
+    PS_CK(cudaMemcpyAsync(host, src, (size_t)bs * ctx->d.dim * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PS_CK(cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
 void ps_cuda_destroy(ps_cuda_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
@@ -1293,6 +1385,7 @@ void ps_cuda_destroy(ps_cuda_ctx *ctx) {
     for (cudaEvent_t e : ctx->kt_events) cudaEventDestroy(e);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->arch) ps_arch_destroy(ctx->arch);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -1402,6 +1495,7 @@ static int stage_ints(ps_cuda_ctx *ctx, int32_t *dev, int32_t *pinned, const int
 }
 
 int ps_cuda_get_embedding(ps_cuda_ctx *ctx, float *dst, const void *w, int wtype, int64_t dim, const int32_t *tokens, int64_t bs) {
+    PS_NO_ARCH("ps_cuda_get_embedding");
     if (!type_ok(wtype) || dim % blk_elems(wtype)) return fail(ctx, PS_CUDA_ERR_INVALID, "get_embedding: bad type/dim");
     int rc = stage_ints(ctx, ctx->tokens_dev, ctx->h_tokens, tokens, bs);
     if (rc) return rc;
@@ -1418,6 +1512,7 @@ int ps_cuda_rmsnorm(ps_cuda_ctx *ctx, float *dst, const float *x, const float *w
 }
 
 int ps_cuda_matmul(ps_cuda_ctx *ctx, float *dst, const void *w, int wtype, int64_t K, int64_t N, const float *x, int64_t bs) {
+    PS_NO_ARCH("ps_cuda_matmul");
     if (bs <= 0 || N <= 0) return fail(ctx, PS_CUDA_ERR_INVALID, "matmul: empty shape");
     int rc = quantize_act(ctx, wtype, x, K, bs);
     if (rc) return rc;
@@ -1425,6 +1520,7 @@ int ps_cuda_matmul(ps_cuda_ctx *ctx, float *dst, const void *w, int wtype, int64
 }
 
 int ps_cuda_rope(ps_cuda_ctx *ctx, float *dst, const float *src, int64_t head_size, int64_t n_heads, int64_t bs, const int32_t *pos) {
+    PS_NO_ARCH("ps_cuda_rope");
     if (head_size != ctx->d.head_size) return fail(ctx, PS_CUDA_ERR_INVALID, "rope: head_size %lld != model head_size %d", (long long)head_size, ctx->d.head_size);
     for (int64_t i = 0; i < bs; i++)
         if (pos[i] < 0 || pos[i] >= ctx->d.n_ctx) return fail(ctx, PS_CUDA_ERR_INVALID, "rope: position %d outside [0,%d)", pos[i], ctx->d.n_ctx);
@@ -1437,6 +1533,7 @@ int ps_cuda_rope(ps_cuda_ctx *ctx, float *dst, const float *src, int64_t head_si
 }
 
 int ps_cuda_set_rope_freq_factors(ps_cuda_ctx *ctx, const float *factors, int n) {
+    PS_NO_ARCH("ps_cuda_set_rope_freq_factors");
     std::lock_guard<std::mutex> lock(ctx->mu);
     if (factors && n != ctx->d.rope_n_dims / 2) return fail(ctx, PS_CUDA_ERR_INVALID, "rope_freq_factors: %d entries, expected rope_n_dims / 2 = %d", n, ctx->d.rope_n_dims / 2);
     for (int i = 0; factors && i < n; i++)
@@ -1576,6 +1673,7 @@ static int kv_slot_ck(ps_cuda_ctx *ctx, const char *what, int idx, int limit) {
     return 0;
 }
 int ps_cuda_kv_copy_slot(ps_cuda_ctx *ctx, int dst_cache_index, int src_token_index) {
+    PS_NO_ARCH("ps_cuda_kv_copy_slot");
     int rc;
     if ((rc = kv_slot_ck(ctx, "kv_copy_slot (cache index)", dst_cache_index, ctx->d.n_ctx))) return rc;
     if ((rc = kv_slot_ck(ctx, "kv_copy_slot (token of the last batch)", src_token_index, ctx->last_batch))) return rc;
@@ -1587,6 +1685,7 @@ int ps_cuda_kv_copy_slot(ps_cuda_ctx *ctx, int dst_cache_index, int src_token_in
     return 0;
 }
 int ps_cuda_kv_move_slot(ps_cuda_ctx *ctx, int dst_cache_index, int src_cache_index) {
+    PS_NO_ARCH("ps_cuda_kv_move_slot");
     int rc;
     if ((rc = kv_slot_ck(ctx, "kv_move_slot (dst)", dst_cache_index, ctx->d.n_ctx))) return rc;
     if ((rc = kv_slot_ck(ctx, "kv_move_slot (src)", src_cache_index, ctx->d.n_ctx))) return rc;
@@ -1649,6 +1748,7 @@ static int tc_single(ps_cuda_ctx *ctx, const uint8_t *a_blocks, int n_rows, int 
 }
 
 int ps_cuda_bind_model(ps_cuda_ctx *ctx, const ps_cuda_model_weights *w) {
+    PS_NO_ARCH("ps_cuda_bind_model");
     const ps_cuda_model_desc &d = ctx->d;
     const int64_t qdim = (int64_t)d.n_heads * d.head_size, kvd = (int64_t)d.n_kv_heads * d.head_size;
     auto reg = [&](const ps_cuda_tensor &t, int64_t ne0, int64_t ne1, const void **dev, int *type) -> int {
@@ -2122,6 +2222,15 @@ static int forward_ops_tp(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
 }
 
 
+// a layer-list model's forward pass over the ACTIVE cache set (the executor sees the same staged tokens / positions, cache
+// pointers and launch counter the llama paths use)
+static int arch_forward(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
+    PsArchIO io{ctx->stream, ctx->tokens_dev, ctx->pos_dev, ctx->kc.data(), ctx->vct.data(), &ctx->n_launch};
+    std::string err;
+    const int rc = ps_arch_forward(ctx->arch, io, bs, pos0, lm_head, err);
+    return rc ? fail(ctx, rc, "%s", err.c_str()) : 0;
+}
+
 static int check_forward_args(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos, int bs) {
     if (!ctx->bound) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: no model bound");
     if (bs <= 0 || bs > ctx->d.max_batch) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: batch %d outside [1,%d]", bs, ctx->d.max_batch);
@@ -2147,7 +2256,9 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
     ctx->h2d += (int64_t)bs * 8;
     PS_CK(cudaEventRecord(ctx->ev0, ctx->stream));
     ctx->logits_last = ctx->logits;
-    if (ctx->tp > 1 && bs > 1 && ctx->nccl_comm && ctx->opt_tp_batch) {
+    if (ctx->arch) {
+        rc = arch_forward(ctx, bs, lm_head, pos[0]);
+    } else if (ctx->tp > 1 && bs > 1 && ctx->nccl_comm && ctx->opt_tp_batch) {
         // tensor parallel batch (prefill chunk / verify batch): row-sharded GEMMs, one all-gather per exchange for the whole chunk
         if (lm_head && !ctx->tp_logl) { int rc2 = dev_alloc(ctx, (void **)&ctx->tp_logl, (size_t)ctx->d.max_batch * ctx->vocab_l * 4); if (rc2) return rc2; }
         rc = forward_ops_tp(ctx, bs, lm_head, pos[0]);
@@ -2208,6 +2319,7 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
 // runs per column over its own session's cache.  A session's logits are bit-identical to decoding it alone with batch 1.
 static int refresh_kv_tables(ps_cuda_ctx *ctx) {
     const ps_cuda_model_desc &d = ctx->d;
+    if (ctx->arch) return 0; // the executor takes the active set's pointers with every forward pass
     std::vector<float *> ptrs(2 * (size_t)d.n_layers);
     for (int L = 0; L < d.n_layers; L++) { ptrs[L] = ctx->kc[L]; ptrs[d.n_layers + L] = ctx->vct[L]; }
     PS_CK(cudaMemcpyAsync(ctx->kv_ptrs_dev, ptrs.data(), sizeof(float *) * ptrs.size(), cudaMemcpyHostToDevice, ctx->stream));
@@ -2237,9 +2349,10 @@ int ps_cuda_session_create(ps_cuda_ctx *ctx, int *session_id) {
     ks.kc.resize(d.n_layers); ks.vct.resize(d.n_layers);
     for (int L = 0; L < d.n_layers; L++) {
         int rc;
-        if ((rc = dev_alloc(ctx, (void **)&ks.kc[L], bytes)) || (rc = dev_alloc(ctx, (void **)&ks.vct[L], bytes))) return rc;
-        PS_CK(cudaMemsetAsync(ks.kc[L], 0, bytes, ctx->stream));
-        PS_CK(cudaMemsetAsync(ks.vct[L], 0, bytes, ctx->stream));
+        const size_t kb = ctx->arch ? ctx->kv_k_bytes[L] : bytes, vb = ctx->arch ? ctx->kv_v_bytes[L] : bytes; // layer-list models: the layer's own widths
+        if ((rc = dev_alloc(ctx, (void **)&ks.kc[L], kb)) || (rc = dev_alloc(ctx, (void **)&ks.vct[L], vb))) return rc;
+        PS_CK(cudaMemsetAsync(ks.kc[L], 0, kb, ctx->stream));
+        PS_CK(cudaMemsetAsync(ks.vct[L], 0, vb, ctx->stream));
     }
     ks.slot_mask.assign((size_t)d.n_ctx, 1);
     const int id = ctx->next_session++;
@@ -2295,6 +2408,7 @@ int ps_cuda_session_position(ps_cuda_ctx *ctx, int session_id) {
 int ps_cuda_forward_sessions(ps_cuda_ctx *ctx, const int32_t *session_ids, const int32_t *tokens, int n, int lm_head, float *logits_host, int32_t *greedy_ids) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     const ps_cuda_model_desc &d = ctx->d;
+    PS_NO_ARCH("ps_cuda_forward_sessions");
     if (!ctx->bound) return fail(ctx, PS_CUDA_ERR_INVALID, "forward_sessions: no model bound");
     if (ctx->tp > 1) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "forward_sessions: sessions are single-GPU");
     if (!session_ids || !tokens || n <= 0 || n > d.max_batch) return fail(ctx, PS_CUDA_ERR_INVALID, "forward_sessions: batch %d outside [1,%d]", n, d.max_batch);
@@ -2375,6 +2489,7 @@ int ps_cuda_forward_sessions(ps_cuda_ctx *ctx, const int32_t *session_ids, const
 // CausalLM::Batch::save_kv + advance (src/backend/qnn/causal_models.cpp:353-359): the batch's K / V rows go to cache slots
 // position .. position + bs - 1 (kept aside as well for ps_cuda_kv_copy_slot), which are unmasked, and the position advances by bs.
 int ps_cuda_forward_tree(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos, int bs, const uint8_t *tree_mask, int lm_head, float *logits_host) {
+    PS_NO_ARCH("ps_cuda_forward_tree");
     std::lock_guard<std::mutex> lock(ctx->mu);
     if (!ctx->bound) return fail(ctx, PS_CUDA_ERR_INVALID, "forward_tree: no model bound");
     if (ctx->tp > 1) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "forward_tree: tree batches are single-GPU");
@@ -2451,7 +2566,7 @@ int ps_cuda_decode_greedy(ps_cuda_ctx *ctx, int32_t first_token, int n_steps, in
     ctx->h_tokens[0] = first_token;
     PS_CK(cudaMemcpyAsync(ctx->tokens_dev, ctx->h_tokens, 4, cudaMemcpyHostToDevice, ctx->stream));
     ctx->h2d += 4;
-    if ((ctx->opt_fused && ctx->fused_ok) || ops_graph_usable(ctx) || mv_usable(ctx)) {
+    if (!ctx->arch && ((ctx->opt_fused && ctx->fused_ok) || ops_graph_usable(ctx) || mv_usable(ctx))) {
         int32_t *slot = &ctx->h_ids[4096];
         slot[0] = ctx->position;
         slot[1] = 0;
@@ -2490,7 +2605,7 @@ int ps_cuda_decode_greedy(ps_cuda_ctx *ctx, int32_t first_token, int n_steps, in
         *slot = pos;
         PS_CK(cudaMemcpyAsync(ctx->pos_dev, slot, 4, cudaMemcpyHostToDevice, ctx->stream));
         ctx->h2d += 4;
-        int rc = forward_ops(ctx, 1, 1, pos);
+        int rc = ctx->arch ? arch_forward(ctx, 1, 1, pos) : forward_ops(ctx, 1, 1, pos);
         if (rc) return rc;
         ps_k_argmax<<<1, 1024, 0, ctx->stream>>>(ctx->logits, ctx->d.vocab_size, ctx->ids_dev + s, ctx->tokens_dev);
         PS_LAUNCH_CK();
@@ -2545,6 +2660,7 @@ int ps_cuda_tp_unique_id(void *out128) {
 }
 
 int ps_cuda_tp_export(ps_cuda_ctx *ctx, void *handle64) {
+    PS_NO_ARCH("ps_cuda_tp_export");
     if (ctx->tp <= 1 || !ctx->heap) return fail(ctx, PS_CUDA_ERR_INVALID, "tp_export: not a tensor-parallel context");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is 64 bytes");
     PS_CK(cudaSetDevice(ctx->device));
@@ -2555,6 +2671,7 @@ int ps_cuda_tp_export(ps_cuda_ctx *ctx, void *handle64) {
 }
 
 int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n) {
+    PS_NO_ARCH("ps_cuda_tp_import");
     if (ctx->tp <= 1 || n != ctx->tp) return fail(ctx, PS_CUDA_ERR_INVALID, "tp_import: expected %d handles", ctx->tp);
     PS_CK(cudaSetDevice(ctx->device));
     PS_CK(cudaStreamSynchronize(ctx->stream));
@@ -2618,6 +2735,7 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n) {
 }
 
 int ps_cuda_tp_init(ps_cuda_ctx *ctx, const void *id128) {
+    PS_NO_ARCH("ps_cuda_tp_init");
     if (ctx->tp <= 1) return 0;
     if (!nccl_load()) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "tensor parallelism needs libnccl.so.2 (dlopen failed)");
     if (ctx->nccl_comm) return fail(ctx, PS_CUDA_ERR_INVALID, "tp_init: already initialised");
@@ -2630,6 +2748,7 @@ int ps_cuda_tp_init(ps_cuda_ctx *ctx, const void *id128) {
 }
 
 int ps_cuda_set_option(ps_cuda_ctx *ctx, const char *name, int value) {
+    if (ctx->arch && ps_arch_set_option(ctx->arch, name, value)) return 0;
     if (ctx->g_step) { cudaGraphExecDestroy(ctx->g_step); ctx->g_step = nullptr; }
     if (ctx->g_fwd) { cudaGraphExecDestroy(ctx->g_fwd); ctx->g_fwd = nullptr; }
     if (!strcmp(name, "graph")) ctx->opt_graph = value;
