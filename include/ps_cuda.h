@@ -299,6 +299,9 @@ int ps_cuda_read_trace(ps_cuda_ctx *ctx, long long *host, int n_launches);
 /* host-side restatement of glibc expf used by the device code; exported so CPU-only tests can pin it against libm */
 float ps_cuda_host_expf_ref(float x);
 float ps_cuda_host_v_expf(float x);
+/* host-side distance bucket of a layer-list attention's bias table (rows, rel_max_dist): the table the device reads is built
+ * from this function, so CPU-only tests can pin it */
+int ps_cuda_host_rel_bucket(int distance, int rows, float max_dist);
 
 #ifdef __cplusplus
 }

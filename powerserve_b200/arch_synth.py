@@ -1,0 +1,76 @@
+"""Synthetic layer-list model directories (config.json + model.safetensors, random bfloat16 weights) for tests and
+bench.py - there are no real checkpoints on the build / GPU boxes.  The result loads through `arch.load_model` like any
+other model directory.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import safetensors
+
+
+def nufusun_layer(heads: int, kv_heads: int, dim: int, vdim: int, *, scale: Optional[float] = None, bias_max: float = 100.0,
+                  experts: int = 0, top: int = 1, ff: int = 0, limit: float = 1.0) -> dict:
+    """one entry of a Nufusun config's layer list; experts == 0 means a layer without a feed-forward"""
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5),
+                       "bias_max": bias_max},
+             "mlp": None}
+    if experts:
+        layer["mlp"] = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+    return layer
+
+
+def nufusun_config(width: int, vocab: int, layers: List[dict], *, eps: float = 1e-5, embed_scale: float = 1.0) -> dict:
+    return {"architecture": "Nufusun", "embedding": {"scale": embed_scale}, "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+def nufusun_weights(cfg: dict, seed: int = 0, rel_rows: int = 16, fast: bool = False) -> Dict[str, np.ndarray]:
+    """float32 arrays holding bfloat16-representable values (what the file will hold), keyed by tensor name.
+    fast = True draws the big matrices as random bfloat16 bit patterns of bounded exponent (seconds for gigabytes)."""
+    rng = np.random.default_rng(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def mat(out_dim, in_dim, gain=1.0):
+        if fast:
+            # sign + exponent around 2^-k for the wanted scale + random mantissa; returned as bf16 bit patterns (uint16)
+            s = gain / np.sqrt(in_dim)
+            e = int(np.floor(np.log2(s))) + 127
+            bits = rng.integers(0, 1 << 7, size=(out_dim, in_dim), dtype=np.uint16) | np.uint16(e << 7)
+            bits |= (rng.integers(0, 2, size=(out_dim, in_dim), dtype=np.uint16) << 15).astype(np.uint16)
+            return bits
+        return rnd(rng.standard_normal((out_dim, in_dim), dtype=np.float32) * np.float32(gain / np.sqrt(in_dim)))
+
+    def rnd(a):
+        return (safetensors.float32_to_bf16_bits(a).astype(np.uint32) << 16).view(np.float32)
+
+    t: Dict[str, np.ndarray] = {"embed": mat(V, W, np.sqrt(W)), "final.norm": rnd(rng.standard_normal(W).astype(np.float32) * 0.1), "head": mat(V, W)}
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        H, G, dq, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        t[p + "norm1"] = rnd(rng.standard_normal(W).astype(np.float32) * 0.1)
+        t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * dq, W, 2.0), mat(G * dq, W, 2.0), mat(G * dv, W)
+        t[p + "mix.o"] = mat(W, H * dv)
+        for n, k in (("q", H * dq), ("k", G * dq), ("v", G * dv), ("o", W)):
+            t[p + f"mix.{n}.b"] = rnd(rng.standard_normal(k).astype(np.float32) * 0.1)
+        t[p + "mix.rel"] = rnd(rng.standard_normal((rel_rows, H)).astype(np.float32) * 0.7)
+        t[p + "mix.talk"] = rnd(np.eye(H, dtype=np.float32) + rng.standard_normal((H, H)).astype(np.float32) * 0.2)
+        t[p + "mix.temp"] = rnd(1.0 + rng.standard_normal(H).astype(np.float32) * 0.2)
+        if l.get("mlp") is not None:
+            E, ff = l["mlp"]["router"]["experts"], l["mlp"]["expert"]["ff"]
+            t[p + "mlp.router"] = mat(E, W, 2.0)
+            for e in range(E):
+                t[p + f"mlp.e{e}.gate"], t[p + f"mlp.e{e}.up"], t[p + f"mlp.e{e}.down"] = mat(ff, W, 1.5), mat(ff, W, 1.5), mat(W, ff)
+    return t
+
+
+def write_model_dir(path: str, cfg: dict, tensors: Dict[str, np.ndarray]) -> str:
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+    safetensors.write_file(os.path.join(path, "model.safetensors"), tensors)
+    return path

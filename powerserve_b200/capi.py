@@ -147,6 +147,7 @@ def load_library() -> C.CDLL:
         "ps_cuda_read_trace": (ci, [vp, C.c_void_p, ci]),
         "ps_cuda_host_expf_ref": (C.c_float, [C.c_float]),
         "ps_cuda_host_v_expf": (C.c_float, [C.c_float]),
+        "ps_cuda_host_rel_bucket": (ci, [ci, ci, C.c_float]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)   # AttributeError here == the library does not export what include/ps_cuda.h declares

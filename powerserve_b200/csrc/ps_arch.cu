@@ -144,6 +144,13 @@ size_t pa_decode_smem(int H, int dq, int dv) { return 4 * ((size_t)H * dq + 2 * 
 
 } // namespace
 
+extern "C" int ps_cuda_host_rel_bucket(int distance, int rows, float max_dist) {
+    if (distance < 0 || rows < 2 || !(max_dist > (float)(rows / 2))) return -1;
+    std::vector<uint16_t> t;
+    build_bucket_table(rows, max_dist, distance + 1, t);
+    return (int)t[(size_t)distance];
+}
+
 int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err) {
     *out = nullptr;
     const ps_cuda_arch_desc &d = *desc;
