@@ -20,6 +20,7 @@
 typedef __nv_bfloat16 bf16;
 
 #include "ps_arch_kernels.cuh"
+#include "ps_arch_tc.cuh"
 
 // ====================================================================================================================== host
 struct PsArchLayer {
@@ -28,6 +29,8 @@ struct PsArchLayer {
     bf16 *wqkv = nullptr, *wo = nullptr, *router = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
     float *bqkv = nullptr, *bo = nullptr, *norm = nullptr, *rel = nullptr, *mix = nullptr, *temp = nullptr;
     uint16_t *bucket = nullptr; // distance -> row of the bias table, n_ctx entries
+    // tensor-core operand blocks of the matrices (bfloat16 compute only): q|k|v, o, gate, up, down (per expert)
+    uint8_t *t_qkv = nullptr, *t_o = nullptr, *t_gate = nullptr, *t_up = nullptr, *t_down = nullptr;
 };
 
 struct PsArch {
@@ -46,6 +49,9 @@ struct PsArch {
     int max_qkv = 0, max_od = 0, max_h = 0, max_top = 0, max_ff = 0, max_e = 0, max_dv = 0;
     int taps_on = 0;
     std::vector<float *> taps;
+    uint8_t *t_head = nullptr, *tcx = nullptr; // lm_head operand blocks; activation blocks of the current product
+    int max_k = 0;
+    int opt_tc = 1;     // bfloat16 batches (bs >= 2) run on the tcgen05 GEMM; 0 = the fp32-FMA tile kernels on rounded operands
     int opt_simple = 0; // 1: every batch width takes the tiled kernels (the single-token kernels are skipped; tests compare the two)
     int n_sm = 148;
 };
@@ -183,10 +189,12 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         a->max_od = std::max(a->max_od, w.od);
         a->max_h = std::max(a->max_h, l.n_heads);
         a->max_dv = std::max(a->max_dv, l.v_dim);
+        a->max_k = std::max(a->max_k, std::max(d.dim, w.od));
         if (l.mlp_kind == PS_MLP_ROUTED) {
             a->max_top = std::max(a->max_top, l.top_k);
             a->max_ff = std::max(a->max_ff, l.expert_ff);
             a->max_e = std::max(a->max_e, l.n_experts);
+            a->max_k = std::max(a->max_k, l.expert_ff);
         }
     }
     a->d.layers = nullptr; // the caller's array need not outlive this call: the copies live in L
@@ -210,6 +218,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     AL(a->row_token, 4 * nrow);
     AL(a->row_slot, 4 * nrow);
     const size_t ntile = nrow / PA_TM + (size_t)std::max(a->max_e, 1) + 1;
+    if (a->round) AL(a->tcx, (nrow / PT_N + (size_t)std::max(a->max_e, 1) + 1) * (size_t)((a->max_k + PT_KB - 1) / PT_KB) * PT_BLOCK);
     AL(a->tile_e, 4 * ntile);
     AL(a->tile_row0, 4 * ntile);
     AL(a->tile_end, 4 * ntile);
@@ -219,9 +228,11 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     int dev = 0;
     cudaGetDevice(&dev);
     { int v = 148; if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) a->n_sm = v; }
-    if (cudaFuncSetAttribute(pa_k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(pa_k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
-        return bail(afail(err, PS_CUDA_ERR_CUDA, "cudaFuncSetAttribute(decode attention shared memory) failed"));
+        return bail(afail(err, PS_CUDA_ERR_CUDA, "cudaFuncSetAttribute(dynamic shared memory) failed"));
     }
     *out = a;
     return 0;
@@ -241,6 +252,7 @@ const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 
 int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
+    if (!strcmp(name, "arch_tc")) { a->opt_tc = value; return 1; }
     return 0;
 }
 
@@ -306,6 +318,27 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                     return rc;
         }
     }
+    if (a->round) {
+        // tensor-core operand blocks: every matrix once more in the layout the tcgen05 GEMM streams (ps_arch_tc.cuh)
+        auto tile = [&](uint8_t **dst, const bf16 *src, int groups, int N, int K) -> int {
+            const int n_rt = (N + PT_M - 1) / PT_M, nkb = (K + PT_KB - 1) / PT_KB;
+            int r = aalloc(a, (void **)dst, (size_t)groups * n_rt * nkb * PT_BLOCK, err);
+            if (r) return r;
+            pa_k_tc_tile_w<<<dim3((unsigned)nkb, (unsigned)n_rt, (unsigned)groups), 256, 0, stream>>>(*dst, src, N, K, n_rt, nkb);
+            PA_CK(cudaGetLastError());
+            return 0;
+        };
+        if ((rc = tile(&a->t_head, a->head, 1, d.vocab_size, d.dim))) return rc;
+        for (int i = 0; i < d.n_layers; i++) {
+            PsArchLayer &w = a->L[(size_t)i];
+            if ((rc = tile(&w.t_qkv, w.wqkv, 1, w.qd + w.kd + w.vd, d.dim)) || (rc = tile(&w.t_o, w.wo, 1, d.dim, w.od))) return rc;
+            if (w.d.mlp_kind == PS_MLP_ROUTED &&
+                ((rc = tile(&w.t_gate, w.wgate, w.d.n_experts, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, w.d.n_experts, w.d.expert_ff, d.dim)) ||
+                 (rc = tile(&w.t_down, w.wdown, w.d.n_experts, d.dim, w.d.expert_ff))))
+                return rc;
+        }
+        PA_CK(cudaStreamSynchronize(stream));
+    }
     a->bound = true;
     return 0;
 }
@@ -319,6 +352,18 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     const dim3 blk(256);
     auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
     const bool single = bs == 1 && !a->opt_simple;
+    const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
+    // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
+    auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
+        const int nkb = (K + PT_KB - 1) / PT_KB, n_ct = (M + PT_N - 1) / PT_N, n_rt = (N + PT_M - 1) / PT_M;
+        pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, X, ldx, M, K, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
+        PA_LAUNCH();
+        PtArgs g{};
+        g.a0 = wt; g.b = a->tcx; g.nkb = nkb; g.n_rt = n_rt; g.n_ct = n_ct; g.M = M; g.N = N; g.mode = PT_MODE_DENSE; g.C = C; g.ldc = ldc; g.bias = bias; g.err = io.err_dev;
+        pa_k_tc_gemm<1><<<std::min(a->n_sm, n_ct * n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+        PA_LAUNCH();
+        return 0;
+    };
 
     pa_k_embed<<<bs, 128, 0, st>>>(a->x, a->embed, io.tokens_dev, dim, d.embed_scale);
     PA_LAUNCH();
@@ -331,6 +376,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         // ---- token mixer: projections -> cache -> scores -> (mix, soft-max) -> P.V -> output projection
         if (single) {
             pa_k_matvec<ROUND><<<cdiv(nqkv, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, w.wqkv, w.bqkv, a->qkv, nqkv, dim);
+        } else if (tc) {
+            int rc = tc_dense(a->h, dim, bs, dim, w.t_qkv, nqkv, w.bqkv, a->qkv, nqkv);
+            if (rc) return rc;
         } else {
             pa_k_linear<ROUND><<<dim3(cdiv(nqkv, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wqkv, w.bqkv, a->qkv, nqkv, bs, nqkv, dim);
         }
@@ -357,6 +405,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         }
         if (single) {
             pa_k_matvec<ROUND><<<cdiv(dim, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->att, w.wo, w.bo, a->ao, dim, w.od);
+        } else if (tc) {
+            int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
+            if (rc) return rc;
         } else {
             pa_k_linear<ROUND><<<dim3(cdiv(dim, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->att, w.od, w.wo, w.bo, a->ao, dim, bs, dim, w.od);
         }
@@ -374,9 +425,30 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 PA_LAUNCH();
                 pa_k_expert_down_mv<ROUND><<<dim3(cdiv(dim, PA_MV_ROWS), top), PA_MV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, w.wdown, a->slot, dim, ff, l.route_on_input);
                 PA_LAUNCH();
+            } else if (tc) {
+                const int max_tiles = n / PT_N + E + 1, nkb1 = (dim + PT_KB - 1) / PT_KB, nkb2 = (ff + PT_KB - 1) / PT_KB;
+                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PT_N, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
+                PA_LAUNCH();
+                pa_k_tc_prep_x<<<dim3((unsigned)nkb1, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, a->h, dim, n, dim, nkb1, a->n_tiles, a->tile_row0, a->tile_end, a->row_token,
+                                                                                        l.route_on_input ? a->row_w : nullptr);
+                PA_LAUNCH();
+                PtArgs g{};
+                g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb1; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = max_tiles; g.n_ct_dev = a->n_tiles;
+                g.tile_e = a->tile_e; g.tile_row0 = a->tile_row0; g.tile_end = a->tile_end; g.M = n; g.N = ff; g.mode = PT_MODE_EXPERT_UP; g.C = a->y; g.ldc = ff;
+                g.limit = l.act_limit; g.alpha = l.act_alpha; g.shift = l.up_shift; g.err = io.err_dev;
+                pa_k_tc_gemm<2><<<std::min(a->n_sm, max_tiles * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+                PA_LAUNCH();
+                pa_k_tc_prep_x<<<dim3((unsigned)nkb2, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, a->y, ff, n, ff, nkb2, a->n_tiles, a->tile_row0, a->tile_end, nullptr, nullptr);
+                PA_LAUNCH();
+                PtArgs g2{};
+                g2.a0 = w.t_down; g2.b = a->tcx; g2.nkb = nkb2; g2.n_rt = (dim + PT_M - 1) / PT_M; g2.n_ct = max_tiles; g2.n_ct_dev = a->n_tiles;
+                g2.tile_e = a->tile_e; g2.tile_row0 = a->tile_row0; g2.tile_end = a->tile_end; g2.M = n; g2.N = dim; g2.mode = PT_MODE_EXPERT_DOWN; g2.C = a->slot; g2.ldc = dim;
+                g2.row_token = a->row_token; g2.row_slot = a->row_slot; g2.row_w = a->row_w; g2.top = top; g2.on_input = l.route_on_input; g2.err = io.err_dev;
+                pa_k_tc_gemm<1><<<std::min(a->n_sm, max_tiles * g2.n_rt), PT_THREADS, PT_SMEM, st>>>(g2);
+                PA_LAUNCH();
             } else {
                 const int max_tiles = n / PA_TM + E + 1;
-                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
+                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PA_TM, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
                 PA_LAUNCH();
                 pa_k_expert_up<ROUND><<<dim3(cdiv(ff, PA_TN), max_tiles), blk, 0, st>>>(a->h, dim, a->row_token, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles,
                                                                                         w.wgate, w.wup, a->y, ff, dim, l.route_on_input, l.act_limit, l.act_alpha, l.up_shift);
@@ -398,6 +470,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         PA_LAUNCH();
         if (single) {
             pa_k_matvec<ROUND><<<cdiv(d.vocab_size, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, a->head, nullptr, a->logits, d.vocab_size, dim);
+        } else if (tc) {
+            int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);
+            if (rc) return rc;
         } else {
             pa_k_linear<ROUND><<<dim3(cdiv(d.vocab_size, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, a->head, nullptr, a->logits, d.vocab_size, bs, d.vocab_size, dim);
         }

@@ -17,6 +17,7 @@ struct PsArchIO {
     float *const *kc;          // per layer: K rows  [n_ctx][n_kv_heads * qk_dim]
     float *const *vct;         // per layer: V^T rows [n_kv_heads * v_dim][n_ctx]
     int64_t *n_launch;         // the context's kernel-launch counter
+    int *err_dev;              // the context's device-side failure flags ([0]: a tensor-core pipeline wait gave up)
 };
 
 int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err);

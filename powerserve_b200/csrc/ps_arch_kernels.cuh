@@ -224,8 +224,8 @@ __global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, 
     }
 }
 
-// (token, slot) pairs grouped by expert: row lists + the table of 64-row tiles the expert kernels walk
-__global__ void __launch_bounds__(256) pa_k_dispatch(const int *__restrict__ sel_e, const float *__restrict__ sel_w, int n, int top, int E, int *__restrict__ row_token,
+// (token, slot) pairs grouped by expert: row lists + the table of row tiles (tile_rows each, the last of an expert ragged) the expert kernels walk
+__global__ void __launch_bounds__(256) pa_k_dispatch(const int *__restrict__ sel_e, const float *__restrict__ sel_w, int n, int top, int E, int tile_rows, int *__restrict__ row_token,
                                                      int *__restrict__ row_slot, float *__restrict__ row_w, int *__restrict__ tile_e, int *__restrict__ tile_row0,
                                                      int *__restrict__ tile_end, int *__restrict__ n_tiles) {
     __shared__ int cnt[PA_MAX_EXPERTS], off[PA_MAX_EXPERTS], fill[PA_MAX_EXPERTS];
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(256) pa_k_dispatch(const int *__restrict__ sel
         int o = 0, nt = 0;
         for (int e = 0; e < E; e++) {
             off[e] = o;
-            for (int r = 0; r < cnt[e]; r += PA_TM) { tile_e[nt] = e; tile_row0[nt] = o + r; tile_end[nt] = o + cnt[e]; nt++; }
+            for (int r = 0; r < cnt[e]; r += tile_rows) { tile_e[nt] = e; tile_row0[nt] = o + r; tile_end[nt] = o + cnt[e]; nt++; }
             o += cnt[e];
         }
         *n_tiles = nt;

@@ -2225,7 +2225,7 @@ static int forward_ops_tp(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
 // a layer-list model's forward pass over the ACTIVE cache set (the executor sees the same staged tokens / positions, cache
 // pointers and launch counter the llama paths use)
 static int arch_forward(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
-    PsArchIO io{ctx->stream, ctx->tokens_dev, ctx->pos_dev, ctx->kc.data(), ctx->vct.data(), &ctx->n_launch};
+    PsArchIO io{ctx->stream, ctx->tokens_dev, ctx->pos_dev, ctx->kc.data(), ctx->vct.data(), &ctx->n_launch, ctx->err_dev};
     std::string err;
     const int rc = ps_arch_forward(ctx->arch, io, bs, pos0, lm_head, err);
     return rc ? fail(ctx, rc, "%s", err.c_str()) : 0;

@@ -4,41 +4,10 @@
 // table-op kernels in ps_kernels.cuh (tests/test_gpu_decode.py proves it op by op and end to end).
 #pragma once
 #include "ps_kernels.cuh"
+#include "ps_ptx.cuh"
 
 enum { PS_EPI_STORE = 0, PS_EPI_RESIDUAL = 1, PS_EPI_SILU = 2 };
 
-// ---------------------------------------------------------------------------------------------------- PTX helpers
-PS_D uint32_t ps_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-PS_D void ps_mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ps_smem_u32(bar)), "r"(count));
-}
-PS_D void ps_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ps_smem_u32(bar)), "r"(bytes) : "memory");
-}
-PS_D void ps_mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ps_smem_u32(bar)) : "memory");
-}
-PS_D void ps_mbar_wait(uint64_t *bar, uint32_t parity) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "WAIT_%=:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
-        "@p bra DONE_%=;\n\t"
-        "bra WAIT_%=;\n\t"
-        "DONE_%=:\n\t}" ::"r"(ps_smem_u32(bar)),
-        "r"(parity)
-        : "memory");
-}
-// 1-D TMA: global -> shared, completion counted in bytes on an mbarrier
-PS_D void ps_bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(ps_smem_u32(dst_smem)),
-                 "l"(src_gmem), "r"(bytes), "r"(ps_smem_u32(bar))
-                 : "memory");
-}
-PS_D void ps_fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-PS_D void ps_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-PS_D void ps_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-PS_D void ps_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 PS_D long long ps_globaltimer() {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

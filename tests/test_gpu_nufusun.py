@@ -215,6 +215,26 @@ def test_single_token_kernels_match_the_tiled_ones(tmp_path):
         m.close()
 
 
+def test_tensor_core_gemm_matches_the_tile_kernels(tmp_path):
+    """bfloat16 batches: the tcgen05 GEMM (dense, fused gate|up, down with scatter) against the fp32-FMA tile kernels on the same
+    rounded operands - several row tiles, several column tiles, K not a multiple of the k block, experts with ragged row lists"""
+    layers = [L(6, 3, 24, 20, bias_max=30.0, experts=5, top=2, ff=200, limit=1.2), L(4, 2, 40, 24, bias_max=11.0, experts=3, top=3, ff=72)]
+    d, cfg, t = make(tmp_path, layers, width=136, vocab=300, seed=14, rel_rows=10)
+    toks = tokens(300, 300, 14)
+    m = arch.load_model(d, dtype="bfloat16", max_batch=160, n_ctx=304)
+    n0 = m.be.counter("kernel_launches")
+    a = run(m, toks)
+    n1 = m.be.counter("kernel_launches")
+    m.be.set_option("arch_tc", 0)
+    b = run(m, toks)
+    n2 = m.be.counter("kernel_launches")
+    assert n1 - n0 > n2 - n1                                    # the tensor-core path adds its operand-tiling launches: it did run
+    e = rel_err(a, b)
+    assert np.median(e) < 2e-4 and (e > 2e-3).sum() <= 3, (np.median(e), e.max())
+    check(a, R.forward(cfg, t, toks), "bfloat16", "tensor-core path against the oracle")
+    m.close()
+
+
 def test_sessions_interleaved_and_slots_reused(tmp_path):
     d, cfg, t = make(tmp_path, MIXED, width=72, vocab=130, seed=8, rel_rows=10)
     reqs = [tokens(130, n, 20 + i) for i, n in enumerate((50, 9, 33, 64))]
