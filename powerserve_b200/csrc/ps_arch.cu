@@ -20,6 +20,7 @@
 typedef __nv_bfloat16 bf16;
 
 #include "ps_arch_kernels.cuh"
+#include "ps_arch_decode.cuh"
 #include "ps_arch_tc.cuh"
 
 // ====================================================================================================================== host
@@ -44,7 +45,7 @@ struct PsArch {
     float *x = nullptr, *h = nullptr, *qkv = nullptr, *att = nullptr, *ao = nullptr, *S = nullptr, *logits = nullptr;
     float *y = nullptr, *slot = nullptr, *sel_w = nullptr, *row_w = nullptr;
     int *sel_e = nullptr, *row_token = nullptr, *row_slot = nullptr, *tile_e = nullptr, *tile_row0 = nullptr, *tile_end = nullptr, *n_tiles = nullptr;
-    float *part = nullptr; // decode attention partials
+    float *z = nullptr;    // router logits of the single-token step
     int64_t ldS = 0;
     int max_qkv = 0, max_od = 0, max_h = 0, max_top = 0, max_ff = 0, max_e = 0, max_dv = 0;
     int taps_on = 0;
@@ -145,8 +146,13 @@ void build_bucket_table(int rows, float dmax, int n, std::vector<uint16_t> &t) {
     }
 }
 
-// shared memory of the decode attention: q, two score chunks, the mixing matrix, three per-head vectors, the value sums
-size_t pa_decode_smem(int H, int dq, int dv) { return 4 * ((size_t)H * dq + 2 * (size_t)PA_DEC_CHUNK * H + (size_t)H * H + 3 * (size_t)H + (size_t)H * dv); }
+// shared memory of the single-token kernels
+size_t pa_dec_scores_smem(int H, int G, int dq) { return 4 * ((size_t)PA_DS_KEYS * G * dq + (size_t)H * dq + (size_t)PA_DS_KEYS * H + (size_t)H * H); }
+int pa_dec_pv_chunk(int H, int G) { return std::max(32, (PA_DP_FLOATS / (PA_DP_DIMS + H / G)) & ~31); }
+size_t pa_dec_pv_smem(int H, int G) {
+    const int rep = H / G;
+    return 4 * ((size_t)(PA_DP_DIMS + rep) * pa_dec_pv_chunk(H, G) + (size_t)(2 + 8) * rep);
+}
 
 } // namespace
 
@@ -182,8 +188,8 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         if (l.mlp_kind == PS_MLP_ROUTED && (l.n_experts <= 0 || l.n_experts > PA_MAX_EXPERTS || l.top_k <= 0 || l.top_k > l.n_experts || l.expert_ff <= 0 || l.router_act != 1))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported routed feed-forward (%d experts, top %d, ff %d, router activation %d)", i, l.n_experts,
                               l.top_k, l.expert_ff, l.router_act));
-        if (pa_decode_smem(l.n_heads, l.qk_dim, l.v_dim) > 200 * 1024)
-            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of sizes %d / %d exceed the decode attention's shared memory", i, l.n_heads, l.qk_dim, l.v_dim));
+        if (pa_dec_scores_smem(l.n_heads, l.n_kv_heads, l.qk_dim) > 160 * 1024 || (size_t)d.dim * 4 > 160 * 1024)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of size %d (or width %d) exceed the single-token kernels' shared memory", i, l.n_heads, l.qk_dim, d.dim));
         w.qd = l.n_heads * l.qk_dim; w.kd = l.n_kv_heads * l.qk_dim; w.vd = l.n_kv_heads * l.v_dim; w.od = l.n_heads * l.v_dim;
         a->max_qkv = std::max(a->max_qkv, w.qd + w.kd + w.vd);
         a->max_od = std::max(a->max_od, w.od);
@@ -223,12 +229,17 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     AL(a->tile_row0, 4 * ntile);
     AL(a->tile_end, 4 * ntile);
     AL(a->n_tiles, 16);
-    AL(a->part, 4 * (size_t)PA_DEC_SPLITS * a->max_h * ((size_t)a->max_dv + 2));
+    AL(a->z, 4 * (size_t)std::max(a->max_e, 1));
     if (rc) return bail(rc);
     int dev = 0;
     cudaGetDevice(&dev);
     { int v = 148; if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) a->n_sm = v; }
-    if (cudaFuncSetAttribute(pa_k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+    if (cudaFuncSetAttribute(pa_k_dec_scores, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_pv, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_mv<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_mv<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_expert_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_expert_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
@@ -249,6 +260,7 @@ size_t ps_arch_v_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(si
 float *ps_arch_logits(PsArch *a) { return a->logits; }
 void ps_arch_set_taps(PsArch *a, int on) { a->taps_on = on; }
 const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 0 && (size_t)layer < a->taps.size()) ? a->taps[(size_t)layer] : nullptr; }
+bool ps_arch_step_replayable(const PsArch *a) { return !a->opt_simple && !a->taps_on; }
 int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
@@ -348,10 +360,17 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     const ps_cuda_arch_desc &d = a->d;
     const int dim = d.dim, B = d.max_batch;
     const int n_kv = pos0 + bs;
+    const int n_kv_cap = io.n_kv_cap > 0 ? io.n_kv_cap : n_kv; // grids of the single-token attention (a captured step covers the whole cache)
     cudaStream_t st = io.stream;
     const dim3 blk(256);
     auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
     const bool single = bs == 1 && !a->opt_simple;
+    // warps sharing a row pair in the single-token mat-vecs: enough CTAs to fill the GPU when the matrix has few rows
+    auto pick_ksplit = [&](int rows, int K) {
+        int ks = 1;
+        while (ks < 8 && (rows + 16 / ks - 1) / (16 / ks) < 4 * a->n_sm && K % (16 * ks) == 0 && K / (2 * ks) >= 256) ks *= 2;
+        return ks;
+    };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
     auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
@@ -371,11 +390,19 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
         const int H = l.n_heads, G = l.n_kv_heads, dq = l.qk_dim, dv = l.v_dim, nqkv = w.qd + w.kd + w.vd;
-        pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, w.norm, dim, d.norm_eps);
-        PA_LAUNCH();
+        const bool routed = l.mlp_kind == PS_MLP_ROUTED;
+        if (!single) { // (the single-token kernels norm in their prologues)
+            pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, w.norm, dim, d.norm_eps);
+            PA_LAUNCH();
+        }
         // ---- token mixer: projections -> cache -> scores -> (mix, soft-max) -> P.V -> output projection
         if (single) {
-            pa_k_matvec<ROUND><<<cdiv(nqkv, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, w.wqkv, w.bqkv, a->qkv, nqkv, dim);
+            PaMv mv{};
+            mv.x = a->x; mv.norm_w = w.norm; mv.eps = d.norm_eps; mv.W = w.wqkv; mv.bias = w.bqkv; mv.N = nqkv; mv.K = dim; mv.y = a->qkv;
+            mv.qd = w.qd; mv.kd = w.kd; mv.vd = w.vd; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
+            if (routed) { mv.Wr = w.router; mv.E = l.n_experts; mv.z = a->z; }
+            mv.ksplit = pick_ksplit(nqkv + mv.E, dim);
+            pa_k_dec_mv<ROUND><<<cdiv(nqkv + mv.E, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, w.t_qkv, nqkv, w.bqkv, a->qkv, nqkv);
             if (rc) return rc;
@@ -383,17 +410,17 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             pa_k_linear<ROUND><<<dim3(cdiv(nqkv, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wqkv, w.bqkv, a->qkv, nqkv, bs, nqkv, dim);
         }
         PA_LAUNCH();
-        pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
-        PA_LAUNCH();
+        if (!single) {
+            pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            PA_LAUNCH();
+        }
         PaAttn at;
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
         at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B;
         if (single) {
-            const int splits = std::min<int>(PA_DEC_SPLITS, (n_kv + PA_DEC_CHUNK - 1) / PA_DEC_CHUNK);
-            const size_t smem = pa_decode_smem(H, dq, dv);
-            pa_k_attn_decode<<<splits, 256, smem, st>>>(at, a->qkv, io.kc[li], io.vct[li], io.pos_dev, a->part, splits);
+            pa_k_dec_scores<<<cdiv(n_kv_cap, PA_DS_KEYS), 256, pa_dec_scores_smem(H, G, dq), st>>>(at, a->qkv, io.kc[li], io.pos_dev, a->S, io.err_dev);
             PA_LAUNCH();
-            pa_k_attn_decode_merge<<<H, 128, 0, st>>>(at, a->part, splits, a->att);
+            pa_k_dec_pv<<<dim3(cdiv(dv, PA_DP_DIMS), G), 256, pa_dec_pv_smem(H, G), st>>>(at, a->S, io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();
         } else {
             pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs);
@@ -404,7 +431,11 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             PA_LAUNCH();
         }
         if (single) {
-            pa_k_matvec<ROUND><<<cdiv(dim, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->att, w.wo, w.bo, a->ao, dim, w.od);
+            PaMv mv{};
+            mv.x = a->att; mv.W = w.wo; mv.bias = w.bo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
+            if (!routed) mv.residual = a->x; // no feed-forward: the layer ends here
+            mv.ksplit = pick_ksplit(dim, w.od);
+            pa_k_dec_mv<ROUND><<<cdiv(dim, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 0, st>>>(mv);
         } else if (tc) {
             int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
             if (rc) return rc;
@@ -414,16 +445,20 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         PA_LAUNCH();
         // ---- routed feed-forward on the same normed input
         int top = 0;
-        if (l.mlp_kind == PS_MLP_ROUTED) {
+        if (routed) {
             top = l.top_k;
             const int E = l.n_experts, ff = l.expert_ff, n = bs * top;
-            pa_k_router<<<bs, 256, 0, st>>>(a->h, w.router, dim, E, top, l.route_renorm, a->sel_e, a->sel_w);
-            PA_LAUNCH();
-            if (single) {
-                pa_k_expert_up_mv<ROUND><<<dim3(cdiv(ff, PA_MV_ROWS), top), PA_MV_THREADS, 0, st>>>(a->h, a->sel_e, a->sel_w, w.wgate, w.wup, a->y, ff, dim, l.route_on_input,
-                                                                                                    l.act_limit, l.act_alpha, l.up_shift);
+            if (!single) {
+                pa_k_router<<<bs, 256, 0, st>>>(a->h, w.router, dim, E, top, l.route_renorm, a->sel_e, a->sel_w);
                 PA_LAUNCH();
-                pa_k_expert_down_mv<ROUND><<<dim3(cdiv(dim, PA_MV_ROWS), top), PA_MV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, w.wdown, a->slot, dim, ff, l.route_on_input);
+            }
+            if (single) {
+                (void)n;
+                pa_k_dec_expert_up<ROUND><<<dim3(cdiv(ff, PA_DV_ROWS / 2), top), PA_DV_THREADS, 4 * (size_t)dim, st>>>(
+                    a->x, w.norm, d.norm_eps, a->z, E, top, l.route_renorm, w.wgate, w.wup, a->y, ff, dim, l.route_on_input, l.act_limit, l.act_alpha, l.up_shift, a->sel_e, a->sel_w);
+                PA_LAUNCH();
+                const int ksd = pick_ksplit(dim, ff);
+                pa_k_dec_expert_down<ROUND><<<cdiv(dim, PA_DV_ROWS / ksd), PA_DV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, top, w.wdown, a->ao, a->x, dim, ff, l.route_on_input, ksd);
                 PA_LAUNCH();
             } else if (tc) {
                 const int max_tiles = n / PT_N + E + 1, nkb1 = (dim + PT_KB - 1) / PT_KB, nkb2 = (ff + PT_KB - 1) / PT_KB;
@@ -458,18 +493,25 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 PA_LAUNCH();
             }
         }
-        pa_k_combine<<<dim3(cdiv(dim, 256), bs), 256, 0, st>>>(a->x, a->ao, a->slot, top, dim);
-        PA_LAUNCH();
+        if (!single) {
+            pa_k_combine<<<dim3(cdiv(dim, 256), bs), 256, 0, st>>>(a->x, a->ao, a->slot, top, dim);
+            PA_LAUNCH();
+        }
         if (a->taps_on) {
             if (!a->taps[(size_t)li]) { int rc = aalloc(a, (void **)&a->taps[(size_t)li], 4 * (size_t)dim * B, err); if (rc) return rc; }
             PA_CK(cudaMemcpyAsync(a->taps[(size_t)li], a->x, 4 * (size_t)dim * bs, cudaMemcpyDeviceToDevice, st));
         }
     }
     if (lm_head) {
-        pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, a->final_norm, dim, d.norm_eps);
-        PA_LAUNCH();
+        if (!single) {
+            pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, a->final_norm, dim, d.norm_eps);
+            PA_LAUNCH();
+        }
         if (single) {
-            pa_k_matvec<ROUND><<<cdiv(d.vocab_size, PA_MV_ROWS), PA_MV_THREADS, 0, st>>>(a->h, a->head, nullptr, a->logits, d.vocab_size, dim);
+            PaMv mv{};
+            mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
+            mv.ksplit = pick_ksplit(d.vocab_size, dim);
+            pa_k_dec_mv<ROUND><<<cdiv(d.vocab_size, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);
             if (rc) return rc;

@@ -18,6 +18,7 @@ struct PsArchIO {
     float *const *vct;         // per layer: V^T rows [n_kv_heads * v_dim][n_ctx]
     int64_t *n_launch;         // the context's kernel-launch counter
     int *err_dev;              // the context's device-side failure flags ([0]: a tensor-core pipeline wait gave up)
+    int n_kv_cap;              // > 0: size the single-token attention grid for this many keys (a captured step is replayed at any position)
 };
 
 int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err);
@@ -33,3 +34,5 @@ float *ps_arch_logits(PsArch *a);
 void ps_arch_set_taps(PsArch *a, int on);
 const float *ps_arch_tap(PsArch *a, int layer); // [max_batch][dim] of the last forward, nullptr when taps are off
 int ps_arch_set_option(PsArch *a, const char *name, int value); // 1 = known option
+// the single-token step reads the position from device memory only (it may be captured once and replayed)
+bool ps_arch_step_replayable(const PsArch *a);

@@ -1,0 +1,415 @@
+// ps_arch_decode.cuh - single-token (bs == 1) kernels of the layer-list executor: six launches per layer, every one
+// independent of the position except through device memory, so the step is captured once and replayed as a CUDA graph.
+//
+//   pa_k_dec_mv          weight-streaming mat-vec (bfloat16 rows, 16-byte loads, two rows per warp) with fused prologue / epilogue:
+//                          norm of the residual stream in the prologue (q|k|v + router rows, lm_head),
+//                          bias, K row / V^T column straight into the cache, router logits from the UNROUNDED fp32 input,
+//                          residual add (output projection of a layer without a feed-forward)
+//   pa_k_dec_scores      scores of all heads for 32 keys per CTA (warp per key, coalesced K rows), head mixing, distance bias
+//   pa_k_dec_pv          soft-max statistics (+ sink) per head, weights staged once per CTA, P.V along contiguous V^T rows
+//   pa_k_dec_expert_up   norm + top-k of the router scores in the prologue, gate | up rows of the chosen experts, activation
+//   pa_k_dec_expert_down down rows of the chosen experts summed over the slots + mixer output + residual
+#pragma once
+#include "ps_ptx.cuh"
+
+#define PA_DV_THREADS 256
+#define PA_DV_ROWS 16       // output rows per mat-vec CTA: 8 warps x 2 rows
+#define PA_DS_KEYS 16       // keys per CTA of the decode scores kernel
+#define PA_DP_DIMS 4        // value dims per CTA of the decode P.V kernel (two warps each)
+#define PA_DP_FLOATS 10240  // staged floats per CTA of the P.V kernel: (PA_DP_DIMS + heads per kv head) x chunk keys
+
+// two rows at once: s0 += w0 . f(x), s1 += w1 . f(x) with f = bfloat16 rounding (ROUND) of x * xscale, or identity
+template <bool ROUND>
+__device__ __forceinline__ void pa_dot2(const bf16 *__restrict__ w0, const bf16 *__restrict__ w1, const float *x, int K, float xscale, int lane, float &s0, float &s1,
+                                        int k_begin = 0, int k_end = -1) {
+    s0 = s1 = 0.f;
+    if (k_end < 0) k_end = K;
+    if ((K & 7) == 0 && (k_begin & 7) == 0) {
+#pragma unroll 2
+        for (int k = k_begin + lane * 8; k < k_end; k += 256) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4 *>(w0 + k));
+            const uint4 b = __ldg(reinterpret_cast<const uint4 *>(w1 + k));
+            const float4 x0 = *reinterpret_cast<const float4 *>(x + k), x1 = *reinterpret_cast<const float4 *>(x + k + 4);
+            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const float xa = pa_rnd<ROUND>(xv[2 * t] * xscale), xb = pa_rnd<ROUND>(xv[2 * t + 1] * xscale);
+                s0 = fmaf(__uint_as_float(au[t] << 16), xa, s0);
+                s0 = fmaf(__uint_as_float(au[t] & 0xffff0000u), xb, s0);
+                s1 = fmaf(__uint_as_float(bu[t] << 16), xa, s1);
+                s1 = fmaf(__uint_as_float(bu[t] & 0xffff0000u), xb, s1);
+            }
+        }
+    } else {
+        for (int k = k_begin + lane; k < k_end; k += 32) {
+            const float xa = pa_rnd<ROUND>(x[k] * xscale);
+            s0 = fmaf(__bfloat162float(w0[k]), xa, s0);
+            s1 = fmaf(__bfloat162float(w1[k]), xa, s1);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); s1 += __shfl_xor_sync(0xffffffffu, s1, o); }
+}
+
+// ask L2 for a warp's slice of two weight rows before the prologue's barriers: the stream then starts from L2
+__device__ __forceinline__ void pa_prefetch2(const bf16 *w0, const bf16 *w1, int k_begin, int k_end, int lane) {
+    for (int k = k_begin + lane * 64; k < k_end; k += 32 * 64) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + k));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w1 + k));
+    }
+}
+
+// block-wide: hs[k] = x[k] / sqrt(mean(x^2) + eps) * w[k]  (w holds 1 + weight for unit-offset norms); 256 threads
+__device__ __forceinline__ void pa_norm_to_smem(float *hs, const float *__restrict__ x, const float *__restrict__ w, int dim, float eps) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) s = fmaf(x[c], x[c], s);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
+        inv_s = 1.0f / sqrtf(t / (float)dim + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) hs[c] = x[c] * inv * w[c];
+    __syncthreads();
+}
+
+struct PaMv {
+    const float *x;        // input vector [K]
+    const float *norm_w;   // non-null: the input is normed first (K = model width)
+    float eps;
+    const bf16 *W;         // [N][K]
+    const float *bias;     // [N] or null
+    int N, K;
+    float *y;              // [N] (rows routed to the cache below are not stored here)
+    float *residual;       // non-null: residual[n] += result instead of y[n] = result
+    // q | k | v routing of the rows: [0, qd) -> y, [qd, qd + kd) -> K cache row `pos`, then vd rows -> V^T column `pos` (kd = 0: none)
+    int qd, kd, vd;
+    float *kc, *vct;
+    int n_ctx;
+    const int32_t *pos;
+    // extra fp32-input rows after the N weight rows: router logits z[e] = Wr[e] . h (h unrounded)
+    const bf16 *Wr;
+    int E;
+    float *z;
+    int ksplit;            // warps of a CTA that share a row pair, each taking K / ksplit of the columns (1, 2, 4 or 8)
+};
+
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
+    extern __shared__ __align__(16) float pa_hs[];
+    __shared__ float part_s[8][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ks = a.ksplit, pairs = 8 / ks, pair = warp % pairs, slice = warp / pairs;
+    const int total = a.N + a.E;
+    const int n0 = (blockIdx.x * pairs + pair) * 2, n1 = min(n0 + 1, total - 1);
+    const int kc = a.K / ks, k_begin = slice * kc, k_end = slice == ks - 1 ? a.K : k_begin + kc;
+    const bool live = n0 < total;
+    // rows of the pair: weight rows below N, router rows (fp32 input, never rounded) from N on
+    const bf16 *w0 = nullptr, *w1 = nullptr;
+    if (live) {
+        w0 = n0 < a.N ? a.W + (int64_t)n0 * a.K : a.Wr + (int64_t)(n0 - a.N) * a.K;
+        w1 = n1 < a.N ? a.W + (int64_t)n1 * a.K : a.Wr + (int64_t)(n1 - a.N) * a.K;
+        pa_prefetch2(w0, w1, k_begin, k_end, lane);
+    }
+    const float *xin = a.x;
+    if (a.norm_w) {
+        pa_norm_to_smem(pa_hs, a.x, a.norm_w, a.K, a.eps);
+        xin = pa_hs;
+    }
+    float s0 = 0.f, s1 = 0.f;
+    if (live) {
+        if (n0 >= a.N) {
+            pa_dot2<false>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
+        } else if (n1 >= a.N) { // the pair straddles the two matrices
+            float t;
+            pa_dot2<ROUND>(w0, w0, xin, a.K, 1.0f, lane, s0, t, k_begin, k_end);
+            pa_dot2<false>(w1, w1, xin, a.K, 1.0f, lane, s1, t, k_begin, k_end);
+        } else {
+            pa_dot2<ROUND>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
+        }
+    }
+    if (ks > 1) {
+        if (lane == 0) { part_s[warp][0] = s0; part_s[warp][1] = s1; }
+        __syncthreads();
+        if (slice != 0) return;
+        s0 = s1 = 0.f;
+        for (int q = 0; q < ks; q++) { s0 += part_s[q * pairs + pair][0]; s1 += part_s[q * pairs + pair][1]; }
+    }
+    if (live && lane < 2) {
+        const int n = lane ? n1 : n0;
+        if (lane && n1 == n0) return;
+        float v = lane ? s1 : s0;
+        if (n >= a.N) { a.z[n - a.N] = v; return; }
+        if (a.bias) v += a.bias[n];
+        if (a.kd && n >= a.qd) {
+            const int p = a.pos[0];
+            if (n < a.qd + a.kd) a.kc[(int64_t)p * a.kd + (n - a.qd)] = v;
+            else a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
+        } else if (a.residual) {
+            a.residual[n] += v;
+        } else {
+            a.y[n] = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- decode attention
+// b[h][j] for the CTA's PA_DS_KEYS keys.  The keys' cache rows are ONE contiguous region: a single 1-D bulk copy brings them to
+// shared memory while the threads fetch q and the mixing matrix; then a warp per key forms the raw scores of every head (a kv
+// group's query heads reuse the key element), applies scale / temperature / distance bias, and the heads are mixed.
+__global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *__restrict__ q, const float *__restrict__ kc, const int32_t *__restrict__ pos_dev,
+                                                       float *__restrict__ b, int *__restrict__ err) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ __align__(8) uint64_t bar;
+    const int H = at.H, G = at.G, dq = at.dq, rep = H / G, kd = G * dq;
+    float *ks = sm;                        // [PA_DS_KEYS][kd]
+    float *qs = ks + PA_DS_KEYS * kd;      // [H][dq]
+    float *sa = qs + H * dq;               // [PA_DS_KEYS][H]
+    float *Ts = sa + PA_DS_KEYS * H;       // [H][H]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pos = pos_dev[0], j0 = blockIdx.x * PA_DS_KEYS;
+    if (j0 > pos) return;
+    const int nj = min(PA_DS_KEYS, pos + 1 - j0);
+    const bool bulk = (kd & 3) == 0;
+    if (bulk && tid == 0) {
+        ps_mbar_init(&bar, 1);
+        ps_fence_barrier_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        ps_mbar_expect_tx(&bar, (uint32_t)(nj * kd * 4));
+        ps_bulk_g2s(ks, kc + (int64_t)j0 * kd, (uint32_t)(nj * kd * 4), &bar);
+    }
+    if (!bulk) for (int t = tid; t < nj * kd; t += 256) ks[t] = kc[(int64_t)j0 * kd + t];
+    for (int t = tid; t < H * dq; t += 256) qs[t] = q[t];
+    if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t];
+    __syncthreads();
+    if (bulk && !ps_tc_wait(&bar, 0)) { if (tid == 0) err[0] = 5; return; }
+    for (int jj = warp; jj < nj; jj += 8) {
+        const float *krow = ks + jj * kd;
+        for (int g = 0; g < G; g++) {
+            for (int r0 = 0; r0 < rep; r0 += 4) {
+                float s[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int d = lane; d < dq; d += 32) {
+                    const float kv = krow[g * dq + d];
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+                        if (r0 + r < rep) s[r] = fmaf(kv, qs[(g * rep + r0 + r) * dq + d], s[r]);
+                }
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    if (r0 + r >= rep) break;
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+                }
+                if (lane == 0) {
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+                        if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = pa_score(at, s[r], g * rep + r0 + r, pos - (j0 + jj));
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = tid; t < nj * H; t += 256) {
+        const int h = t / nj, jj = t % nj; // jj fastest: the stores of a head are contiguous
+        float s;
+        if (at.mix) {
+            s = 0.f;
+            for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
+        } else {
+            s = sa[jj * H + h];
+        }
+        b[(int64_t)h * at.ldS + j0 + jj] = s;
+    }
+}
+
+// att[h][c] = sum_j p_hj V^T[g(h) dv + c][j] for one kv head g and PA_DP_DIMS value dims; p = soft-max of b[h][0 .. pos] with the
+// optional sink term.  Phase 1: max and sum of every query head of the group.  Phase 2, per chunk of keys: the CTA's V^T rows
+// arrive by 1-D bulk copies while the threads compute the chunk's weights once into shared memory; two warps per value dim
+// (the halves of the chunk) then run float4 dot products out of shared memory for every head of the group.
+__global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__restrict__ b, const float *__restrict__ vct, const int32_t *__restrict__ pos_dev,
+                                                   float *__restrict__ att, int chunk, int *__restrict__ err) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[8];
+    __shared__ __align__(8) uint64_t bar;
+    const int H = at.H, G = at.G, dv = at.dv, rep = H / G, g = blockIdx.y;
+    float *vs = sm;                         // [PA_DP_DIMS][chunk] V^T rows of the chunk
+    float *ps = vs + PA_DP_DIMS * chunk;    // [rep][chunk] soft-max weights of the chunk (un-normalised)
+    float *ms = ps + rep * chunk;           // [rep] row maxima
+    float *inv = ms + rep;                  // [rep] 1 / denominators
+    float *acc = inv + rep;                 // [8 warps][rep]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = pos_dev[0] + 1;
+    const bool bulk = (at.n_ctx & 3) == 0;
+    if (bulk && tid == 0) {
+        ps_mbar_init(&bar, 1);
+        ps_fence_barrier_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int r = 0; r < rep; r++) {
+        const float *row = b + (int64_t)(g * rep + r) * at.ldS;
+        float mx = at.sink ? 0.f : -INFINITY;
+        for (int j = tid; j < n; j += 256) mx = fmaxf(mx, row[j]);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red[warp] = mx;
+        __syncthreads();
+        mx = red[0];
+        for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w]);
+        __syncthreads();
+        float sum = 0.f;
+        for (int j = tid; j < n; j += 256) sum += expf(row[j] - mx);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.f;
+            for (int w = 0; w < 8; w++) t += red[w];
+            if (at.sink) t += expf(-mx);
+            ms[r] = mx;
+            inv[r] = 1.0f / t;
+        }
+        __syncthreads();
+    }
+    for (int t = tid; t < 8 * rep; t += 256) acc[t] = 0.f;
+    const int dim_l = warp % PA_DP_DIMS, part = warp / PA_DP_DIMS, n_part = 8 / PA_DP_DIMS;
+    const int c0 = blockIdx.x * PA_DP_DIMS;
+    int it = 0;
+    for (int j0 = 0; j0 < n; j0 += chunk, it++) {
+        const int nj = min(chunk, n - j0), nj4 = (nj + 3) & ~3;
+        __syncthreads(); // the previous chunk's buffers are free
+        if (bulk) {
+            if (tid == 0) {
+                const int rows = min(PA_DP_DIMS, dv - c0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the rows were read through the generic proxy
+                ps_mbar_expect_tx(&bar, (uint32_t)(rows * nj4 * 4));
+                for (int cc = 0; cc < rows; cc++) ps_bulk_g2s(vs + cc * chunk, vct + (int64_t)(g * dv + c0 + cc) * at.n_ctx + j0, (uint32_t)(nj4 * 4), &bar);
+            }
+        } else {
+            for (int t = tid; t < PA_DP_DIMS * nj4; t += 256) {
+                const int cc = t / nj4, jj = t % nj4;
+                vs[cc * chunk + jj] = (c0 + cc < dv && jj < nj) ? vct[(int64_t)(g * dv + c0 + cc) * at.n_ctx + j0 + jj] : 0.f;
+            }
+        }
+        for (int t = tid; t < rep * nj4; t += 256) {
+            const int r = t / nj4, jj = t % nj4;
+            ps[r * chunk + jj] = jj < nj ? expf(b[(int64_t)(g * rep + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
+        }
+        __syncthreads();
+        if (bulk && !ps_tc_wait(&bar, it & 1)) { if (tid == 0) err[0] = 6; return; }
+        if (c0 + dim_l < dv) {
+            const float4 *v4 = reinterpret_cast<const float4 *>(vs + dim_l * chunk);
+            for (int r = 0; r < rep; r++) {
+                const float4 *p4 = reinterpret_cast<const float4 *>(ps + r * chunk);
+                float s = 0.f;
+                for (int i = lane + 32 * part; i < nj4 / 4; i += 32 * n_part) {
+                    const float4 v = v4[i], p = p4[i];
+                    s = fmaf(p.x, v.x, s); s = fmaf(p.y, v.y, s); s = fmaf(p.z, v.z, s); s = fmaf(p.w, v.w, s);
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) acc[warp * rep + r] += s;
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = tid; t < PA_DP_DIMS * rep; t += 256) {
+        const int cc = t / rep, r = t % rep;
+        if (c0 + cc >= dv) continue;
+        float s = 0.f;
+        for (int pp = 0; pp < n_part; pp++) s += acc[(pp * PA_DP_DIMS + cc) * rep + r];
+        att[(g * rep + r) * dv + c0 + cc] = s * inv[r];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- routed experts
+// the top_k largest router scores (sigmoid of z, ties: the lower expert), optionally renormalised; one thread
+__device__ __forceinline__ void pa_topk_serial(const float *__restrict__ z, int E, int top, int renorm, float *sc, int *se, float *sw) {
+    for (int e = 0; e < E; e++) sc[e] = 1.0f / (1.0f + expf(-z[e]));
+    float sum = 0.f;
+    for (int r = 0; r < top; r++) {
+        int best = 0;
+        float bv = -1.f;
+        for (int e = 0; e < E; e++)
+            if (sc[e] > bv) { bv = sc[e]; best = e; }
+        se[r] = best;
+        sw[r] = bv;
+        sum += bv;
+        sc[best] = -2.f;
+    }
+    if (renorm)
+        for (int r = 0; r < top; r++) sw[r] /= sum;
+}
+
+// grid (row pairs of ff, top_k): y[r][n] = act(gate_e . z, up_e . z), z = round(w_r * h) (score on the input) or round(h)
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float *__restrict__ x, const float *__restrict__ norm_w, float eps, const float *__restrict__ z, int E,
+                                                                    int top, int renorm, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y,
+                                                                    int ff, int dim, int on_input, float limit, float alpha, float shift, int *__restrict__ sel_e,
+                                                                    float *__restrict__ sel_w) {
+    extern __shared__ __align__(16) float pa_hs[];
+    __shared__ float sc[PA_MAX_EXPERTS];
+    __shared__ int se[PA_MAX_EXPERTS];
+    __shared__ float sw[PA_MAX_EXPERTS];
+    if (threadIdx.x == 0) {
+        pa_topk_serial(z, E, top, renorm, sc, se, sw);
+        if (blockIdx.x == 0 && blockIdx.y == 0)
+            for (int r = 0; r < top; r++) { sel_e[r] = se[r]; sel_w[r] = sw[r]; }
+    }
+    pa_norm_to_smem(pa_hs, x, norm_w, dim, eps); // (its barriers also publish se / sw)
+    const int r = blockIdx.y, e = se[r], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float w = on_input ? sw[r] : 1.0f;
+    // a warp owns one ff row: its gate row and its up row are the pair
+    const int n = blockIdx.x * (PA_DV_ROWS / 2) + warp;
+    if (n >= ff) return;
+    float gsum, usum;
+    pa_dot2<ROUND>(Wg + ((int64_t)e * ff + n) * dim, Wu + ((int64_t)e * ff + n) * dim, pa_hs, dim, w, lane, gsum, usum);
+    if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+}
+
+// x[n] += ao[n] + sum_r down_{e_r}[n] . round(y_r)  (times w_r when the score weighs the output); slots in order; `ksplit`
+// warps share a row pair, each taking ff / ksplit of the columns
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_down(const float *__restrict__ y, const int *__restrict__ sel_e, const float *__restrict__ sel_w, int top,
+                                                                      const bf16 *__restrict__ Wd, const float *__restrict__ ao, float *__restrict__ x, int dim, int ff,
+                                                                      int on_input, int ksplit) {
+    __shared__ float part_s[8][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pairs = 8 / ksplit, pair = warp % pairs, slice = warp / pairs;
+    const int n0 = (blockIdx.x * pairs + pair) * 2, n1 = min(n0 + 1, dim - 1);
+    const int kc = ff / ksplit, k_begin = slice * kc, k_end = slice == ksplit - 1 ? ff : k_begin + kc;
+    const bool live = n0 < dim;
+    float t0 = 0.f, t1 = 0.f;
+    if (live) {
+        for (int r = 0; r < top; r++) {
+            const int e = sel_e[r];
+            pa_prefetch2(Wd + ((int64_t)e * dim + n0) * ff, Wd + ((int64_t)e * dim + n1) * ff, k_begin, k_end, lane);
+        }
+        for (int r = 0; r < top; r++) {
+            const int e = sel_e[r];
+            float s0, s1;
+            pa_dot2<ROUND>(Wd + ((int64_t)e * dim + n0) * ff, Wd + ((int64_t)e * dim + n1) * ff, y + (int64_t)r * ff, ff, 1.0f, lane, s0, s1, k_begin, k_end);
+            const float w = on_input ? 1.0f : sel_w[r];
+            t0 += s0 * w;
+            t1 += s1 * w;
+        }
+    }
+    if (ksplit > 1) {
+        if (lane == 0) { part_s[warp][0] = t0; part_s[warp][1] = t1; }
+        __syncthreads();
+        if (slice != 0) return;
+        t0 = t1 = 0.f;
+        for (int q = 0; q < ksplit; q++) { t0 += part_s[q * pairs + pair][0]; t1 += part_s[q * pairs + pair][1]; }
+    }
+    if (!live) return;
+    if (lane == 0) x[n0] += ao[n0] + t0;
+    if (lane == 1 && n1 != n0) x[n1] += ao[n1] + t1;
+}

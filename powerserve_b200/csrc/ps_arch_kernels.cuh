@@ -2,7 +2,7 @@
 //
 // Tiled kernels (any batch width): one 64 x 64 x 16 fp32 tile core shared by the dense projections, the routed experts
 // (rows gathered per expert), the attention scores (B operand = K cache rows) and P.V (B operand = V^T cache rows).
-// Single-token kernels (bs == 1): warp-per-row bfloat16 mat-vecs and a split-key decode attention with a merge step.
+// The single-token kernels (bs == 1) live in ps_arch_decode.cuh.
 #pragma once
 
 #define PA_TM 64
@@ -11,10 +11,6 @@
 #define PA_LD (PA_TM + 4)
 #define PA_MAX_HEADS 64
 #define PA_MAX_EXPERTS 256
-#define PA_MV_THREADS 256
-#define PA_MV_ROWS 8        // output rows per mat-vec CTA (one warp each)
-#define PA_DEC_SPLITS 64    // at most this many CTAs share the keys of one decode attention
-#define PA_DEC_CHUNK 32     // keys per inner step of the decode attention
 
 struct PaAttn {
     int H, G, dq, dv;
@@ -147,50 +143,6 @@ __global__ void __launch_bounds__(256) pa_k_linear(const float *__restrict__ A, 
     }
 }
 
-// one warp per output row, bs == 1: y[n] = sum_k x[k] W[n][k] + bias[n]
-template <bool ROUND> __device__ __forceinline__ float pa_row_dot(const bf16 *__restrict__ wrow, const float *__restrict__ xs, int K, int lane) {
-    float s = 0.f;
-    if ((K & 7) == 0) {
-        for (int k = lane * 8; k < K; k += 256) {
-            const uint4 raw = *reinterpret_cast<const uint4 *>(wrow + k);
-            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                s = fmaf(__uint_as_float(u[t] << 16), xs[k + 2 * t], s);
-                s = fmaf(__uint_as_float(u[t] & 0xffff0000u), xs[k + 2 * t + 1], s);
-            }
-        }
-    } else {
-        for (int k = lane; k < K; k += 32) s = fmaf(__bfloat162float(wrow[k]), xs[k], s);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    return s;
-}
-
-template <bool ROUND>
-__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_matvec(const float *__restrict__ x, const bf16 *__restrict__ W, const float *__restrict__ bias, float *__restrict__ y, int N, int K) {
-    __shared__ float xs_static[2048];
-    float *xs = K <= 2048 ? xs_static : nullptr;
-    const int lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
-    if (xs) {
-        for (int k = threadIdx.x; k < K; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(x[k]);
-        __syncthreads();
-    }
-    if (n >= N) return;
-    float s;
-    if (xs) {
-        s = pa_row_dot<ROUND>(W + (int64_t)n * K, xs, K, lane);
-    } else { // wide inputs: read (and round) the activation from global memory
-        s = 0.f;
-        const bf16 *wrow = W + (int64_t)n * K;
-        for (int k = lane; k < K; k += 32) s = fmaf(__bfloat162float(wrow[k]), pa_rnd<ROUND>(x[k]), s);
-#pragma unroll
-        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    }
-    if (lane == 0) y[n] = s + (bias ? bias[n] : 0.f);
-}
-
 // ---------------------------------------------------------------------------------------------------------------- router
 // scores = sigmoid(W_r h) in fp32; the top_k largest (ties: the lower expert) -> sel_e / sel_w [token][top_k]
 __global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, const bf16 *__restrict__ Wr, int dim, int E, int top, int renorm, int *__restrict__ sel_e,
@@ -315,63 +267,6 @@ __global__ void __launch_bounds__(256) pa_k_expert_down(const float *__restrict_
     }
 }
 
-// single token: grid (row blocks, top_k); expert ids come from device memory
-template <bool ROUND>
-__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_expert_up_mv(const float *__restrict__ h, const int *__restrict__ sel_e, const float *__restrict__ sel_w,
-                                                                   const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, int on_input,
-                                                                   float limit, float alpha, float shift) {
-    __shared__ float xs[2048];
-    const int r = blockIdx.y, e = sel_e[r], lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
-    const float w = on_input ? sel_w[r] : 1.0f;
-    const bool staged = dim <= 2048;
-    if (staged) {
-        for (int k = threadIdx.x; k < dim; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(h[k] * w);
-        __syncthreads();
-    }
-    if (n >= ff) return;
-    const bf16 *gr = Wg + ((int64_t)e * ff + n) * dim, *ur = Wu + ((int64_t)e * ff + n) * dim;
-    float g, u;
-    if (staged) {
-        g = pa_row_dot<ROUND>(gr, xs, dim, lane);
-        u = pa_row_dot<ROUND>(ur, xs, dim, lane);
-    } else {
-        g = u = 0.f;
-        for (int k = lane; k < dim; k += 32) {
-            const float z = pa_rnd<ROUND>(h[k] * w);
-            g = fmaf(__bfloat162float(gr[k]), z, g);
-            u = fmaf(__bfloat162float(ur[k]), z, u);
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) { g += __shfl_xor_sync(0xffffffffu, g, o); u += __shfl_xor_sync(0xffffffffu, u, o); }
-    }
-    if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(g, u, limit, alpha, shift);
-}
-
-template <bool ROUND>
-__global__ void __launch_bounds__(PA_MV_THREADS) pa_k_expert_down_mv(const float *__restrict__ y, const int *__restrict__ sel_e, const float *__restrict__ sel_w,
-                                                                     const bf16 *__restrict__ Wd, float *__restrict__ slot, int dim, int ff, int on_input) {
-    __shared__ float xs[2048];
-    const int r = blockIdx.y, e = sel_e[r], lane = threadIdx.x & 31, n = blockIdx.x * PA_MV_ROWS + (threadIdx.x >> 5);
-    const float *yr = y + (int64_t)r * ff;
-    const bool staged = ff <= 2048;
-    if (staged) {
-        for (int k = threadIdx.x; k < ff; k += PA_MV_THREADS) xs[k] = pa_rnd<ROUND>(yr[k]);
-        __syncthreads();
-    }
-    if (n >= dim) return;
-    const bf16 *dr = Wd + ((int64_t)e * dim + n) * ff;
-    float s;
-    if (staged) {
-        s = pa_row_dot<ROUND>(dr, xs, ff, lane);
-    } else {
-        s = 0.f;
-        for (int k = lane; k < ff; k += 32) s = fmaf(__bfloat162float(dr[k]), pa_rnd<ROUND>(yr[k]), s);
-#pragma unroll
-        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    }
-    if (lane == 0) slot[(int64_t)r * dim + n] = s * (on_input ? 1.0f : sel_w[r]);
-}
-
 // ---------------------------------------------------------------------------------------------------------------- attention
 __device__ __forceinline__ float pa_score(const PaAttn &at, float dot, int h, int dist) {
     float s = dot * at.scale;
@@ -479,128 +374,5 @@ __global__ void __launch_bounds__(256) pa_k_pv(PaAttn at, const float *__restric
             const int n = n0 + tx * 4 + j;
             if (n < at.dv) att[(int64_t)m * od + h * at.dv + n] = acc[0][i][j];
         }
-    }
-}
-
-// ---- single token: the keys are split over the CTAs; each keeps a running (max, sum, weighted values) per head over chunks of
-// PA_DEC_CHUNK keys - scores of ALL heads for a chunk, mixing, online soft-max, P.V - and leaves its partial for the merge.
-// part[(split * H + h) * (dv + 2)] = {m, l, acc[dv]}
-__global__ void __launch_bounds__(256) pa_k_attn_decode(PaAttn at, const float *__restrict__ qkv, const float *__restrict__ kc, const float *__restrict__ vct,
-                                                        const int32_t *__restrict__ pos_dev, float *__restrict__ part, int splits) {
-    extern __shared__ float sm[];
-    const int H = at.H, G = at.G, dq = at.dq, dv = at.dv, rep = H / G, kd = G * dq;
-    float *qs = sm;                          // [H][dq]
-    float *sa = qs + H * dq;                 // [CHUNK][H] raw scores
-    float *sb = sa + PA_DEC_CHUNK * H;       // [CHUNK][H] mixed scores -> weights
-    float *Ts = sb + PA_DEC_CHUNK * H;       // [H][H]
-    float *ms = Ts + H * H;                  // [H] running max
-    float *ls = ms + H;                      // [H] running sum
-    float *al = ls + H;                      // [H] rescale factor of the step
-    float *acc = al + H;                     // [H][dv]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int pos = pos_dev[0], n = pos + 1;
-    const int per = (n + splits - 1) / splits, j_lo = blockIdx.x * per, j_hi = min(n, j_lo + per);
-    for (int t = tid; t < H * dq; t += 256) qs[t] = qkv[t];
-    if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t];
-    for (int t = tid; t < H; t += 256) { ms[t] = at.sink ? 0.f : -INFINITY; ls[t] = 0.f; }
-    for (int t = tid; t < H * dv; t += 256) acc[t] = 0.f;
-    __syncthreads();
-    for (int j0 = j_lo; j0 < j_hi; j0 += PA_DEC_CHUNK) {
-        const int nj = min(PA_DEC_CHUNK, j_hi - j0);
-        // raw scores: one warp per key, lanes over the key row; every query head of a kv group reuses the loaded value
-        for (int jj = warp; jj < nj; jj += 8) {
-            const float *krow = kc + (int64_t)(j0 + jj) * kd;
-            for (int g = 0; g < G; g++) {
-                for (int r0 = 0; r0 < rep; r0 += 4) {
-                    float s[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int d = lane; d < dq; d += 32) {
-                        const float kv = krow[g * dq + d];
-#pragma unroll
-                        for (int r = 0; r < 4; r++)
-                            if (r0 + r < rep) s[r] = fmaf(kv, qs[(g * rep + r0 + r) * dq + d], s[r]);
-                    }
-#pragma unroll
-                    for (int r = 0; r < 4; r++) {
-                        if (r0 + r >= rep) break;
-#pragma unroll
-                        for (int o = 16; o; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
-                    }
-                    if (lane == 0) {
-#pragma unroll
-                        for (int r = 0; r < 4; r++)
-                            if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = pa_score(at, s[r], g * rep + r0 + r, pos - (j0 + jj));
-                    }
-                }
-            }
-        }
-        __syncthreads();
-        // mix the heads
-        for (int t = tid; t < nj * H; t += 256) {
-            const int jj = t / H, h = t % H;
-            float s;
-            if (at.mix) {
-                s = 0.f;
-                for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
-            } else {
-                s = sa[t];
-            }
-            sb[t] = s;
-        }
-        __syncthreads();
-        // online soft-max bookkeeping: one warp per head
-        for (int h = warp; h < H; h += 8) {
-            float mx = -INFINITY;
-            for (int jj = lane; jj < nj; jj += 32) mx = fmaxf(mx, sb[jj * H + h]);
-#pragma unroll
-            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_old = ms[h], m_new = fmaxf(m_old, mx);
-            float sum = 0.f;
-            for (int jj = lane; jj < nj; jj += 32) {
-                const float e = expf(sb[jj * H + h] - m_new);
-                sb[jj * H + h] = e;
-                sum += e;
-            }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) {
-                const float a = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
-                al[h] = a;
-                ls[h] = ls[h] * a + sum;
-                ms[h] = m_new;
-            }
-        }
-        __syncthreads();
-        // weighted values: one thread per (head, value dim), contiguous along the keys of V^T
-        for (int o = tid; o < H * dv; o += 256) {
-            const int h = o / dv, c = o % dv, g = h / rep;
-            const float *vrow = vct + (int64_t)(g * dv + c) * at.n_ctx + j0;
-            float s = acc[o] * al[h];
-            for (int jj = 0; jj < nj; jj++) s = fmaf(sb[jj * H + h], vrow[jj], s);
-            acc[o] = s;
-        }
-        __syncthreads();
-    }
-    float *out = part + (int64_t)blockIdx.x * H * (dv + 2);
-    for (int t = tid; t < H; t += 256) { out[t * (dv + 2)] = ms[t]; out[t * (dv + 2) + 1] = ls[t]; }
-    for (int o = tid; o < H * dv; o += 256) out[(o / dv) * (dv + 2) + 2 + o % dv] = acc[o];
-}
-
-__global__ void __launch_bounds__(128) pa_k_attn_decode_merge(PaAttn at, const float *__restrict__ part, int splits, float *__restrict__ att) {
-    const int h = blockIdx.x, H = at.H, dv = at.dv;
-    float M = at.sink ? 0.f : -INFINITY;
-    for (int s = 0; s < splits; s++) M = fmaxf(M, part[((int64_t)s * H + h) * (dv + 2)]);
-    float Lsum = at.sink ? expf(-M) : 0.f;
-    for (int s = 0; s < splits; s++) {
-        const float *p = part + ((int64_t)s * H + h) * (dv + 2);
-        if (p[0] != -INFINITY) Lsum += p[1] * expf(p[0] - M);
-    }
-    const float inv = 1.0f / Lsum;
-    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < splits; s++) {
-            const float *p = part + ((int64_t)s * H + h) * (dv + 2);
-            if (p[0] != -INFINITY) v = fmaf(p[2 + c], expf(p[0] - M), v);
-        }
-        att[h * dv + c] = v * inv;
     }
 }

@@ -1046,6 +1046,32 @@ int launch_step(ps_cuda_ctx *ctx, int mode, int n_kv_max) {
 }
 
 // capture one step into a graph (lazily), then replay it
+// a layer-list model's forward pass over the ACTIVE cache set (the executor sees the same staged tokens / positions, cache
+// pointers and launch counter the llama paths use)
+int arch_forward(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0, int n_kv_cap = 0) {
+    PsArchIO io{ctx->stream, ctx->tokens_dev, ctx->pos_dev, ctx->kc.data(), ctx->vct.data(), &ctx->n_launch, ctx->err_dev, n_kv_cap};
+    std::string err;
+    const int rc = ps_arch_forward(ctx->arch, io, bs, pos0, lm_head, err);
+    return rc ? fail(ctx, rc, "%s", err.c_str()) : 0;
+}
+
+// one decode step of a layer-list model as the graph-replayed step builders above it: nothing depends on a host value (the
+// attention grid covers the whole cache, the kernels read the position from device memory), the pick is the shared two-stage
+// arg-max with token feedback and position advance on the device
+int arch_decode_step(ps_cuda_ctx *ctx, bool lm_head, bool pick) {
+    int rc = arch_forward(ctx, 1, lm_head ? 1 : 0, 0, ctx->d.n_ctx);
+    if (rc) return rc;
+    if (lm_head && pick) {
+        const int n_part = std::min(ctx->n_sm, (ctx->d.vocab_size + 255) / 256);
+        ps_k_argmax_parts<<<n_part, 256, 0, ctx->stream>>>(ctx->logits, ctx->d.vocab_size, ctx->part_val, ctx->part_idx);
+        PS_LAUNCH_CK();
+        if ((rc = launch_k(ctx, ps_k_argmax_step, dim3(1), dim3(256), 0, (const float *)ctx->part_val, (const int *)ctx->part_idx, n_part, ctx->ids_dev, ctx->ctr_dev,
+                           ctx->tokens_dev, ctx->pos_dev, (long long *)nullptr, (const PsTpIn *)nullptr))) return rc;
+    }
+    return 0;
+}
+bool arch_graph_usable(ps_cuda_ctx *ctx) { return ctx->arch && ps_arch_step_replayable(ctx->arch); }
+
 int run_step(ps_cuda_ctx *ctx, bool pick, int n_kv_max) {
     if (step_usable(ctx)) {
         const int mode = PS_ST_MODE_LMHEAD | (pick ? PS_ST_MODE_PICK : 0);
@@ -1064,7 +1090,7 @@ int run_step(ps_cuda_ctx *ctx, bool pick, int n_kv_max) {
     }
     const bool ops = ops_graph_usable(ctx);
     const bool mv = mv_usable(ctx);
-    auto build = [&]() { return mv ? decode_step_mv32(ctx, true, pick) : ops ? decode_step_ops(ctx, true, pick) : decode_step_fused(ctx, true, pick); };
+    auto build = [&]() { return ctx->arch ? arch_decode_step(ctx, true, pick) : mv ? decode_step_mv32(ctx, true, pick) : ops ? decode_step_ops(ctx, true, pick) : decode_step_fused(ctx, true, pick); };
     if (!ctx->opt_graph || ctx->opt_ktime) return build();
     cudaGraphExec_t &ge = pick ? ctx->g_step : ctx->g_fwd;
     if (!ge) {
@@ -1311,7 +1337,8 @@ int ps_cuda_create_arch(ps_cuda_ctx **out, int device, const ps_cuda_arch_desc *
     const int64_t B = desc->max_batch;
     if ((rc = ck(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate"))) return bail(rc);
     if ((rc = dev_alloc(ctx, (void **)&ctx->tokens_dev, 4 * B)) || (rc = dev_alloc(ctx, (void **)&ctx->pos_dev, 4 * B)) || (rc = dev_alloc(ctx, (void **)&ctx->ids_dev, 4 * 4096)) ||
-        (rc = dev_alloc(ctx, (void **)&ctx->ctr_dev, 16)) || (rc = dev_alloc(ctx, (void **)&ctx->err_dev, 128)))
+        (rc = dev_alloc(ctx, (void **)&ctx->ctr_dev, 16)) || (rc = dev_alloc(ctx, (void **)&ctx->err_dev, 128)) ||
+        (rc = dev_alloc(ctx, (void **)&ctx->part_val, 4 * 1024)) || (rc = dev_alloc(ctx, (void **)&ctx->part_idx, 4 * 1024)))
         return bail(rc);
     if ((rc = ck(cudaMemsetAsync(ctx->err_dev, 0, 128, ctx->stream), "cudaMemsetAsync"))) return bail(rc);
     ctx->tc_err_dev = ctx->err_dev;
@@ -2222,15 +2249,6 @@ static int forward_ops_tp(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
 }
 
 
-// a layer-list model's forward pass over the ACTIVE cache set (the executor sees the same staged tokens / positions, cache
-// pointers and launch counter the llama paths use)
-static int arch_forward(ps_cuda_ctx *ctx, int bs, int lm_head, int pos0) {
-    PsArchIO io{ctx->stream, ctx->tokens_dev, ctx->pos_dev, ctx->kc.data(), ctx->vct.data(), &ctx->n_launch, ctx->err_dev};
-    std::string err;
-    const int rc = ps_arch_forward(ctx->arch, io, bs, pos0, lm_head, err);
-    return rc ? fail(ctx, rc, "%s", err.c_str()) : 0;
-}
-
 static int check_forward_args(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos, int bs) {
     if (!ctx->bound) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: no model bound");
     if (bs <= 0 || bs > ctx->d.max_batch) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: batch %d outside [1,%d]", bs, ctx->d.max_batch);
@@ -2257,7 +2275,7 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
     PS_CK(cudaEventRecord(ctx->ev0, ctx->stream));
     ctx->logits_last = ctx->logits;
     if (ctx->arch) {
-        rc = arch_forward(ctx, bs, lm_head, pos[0]);
+        rc = (bs == 1 && lm_head && arch_graph_usable(ctx)) ? run_step(ctx, false, pos[0] + 1) : arch_forward(ctx, bs, lm_head, pos[0]);
     } else if (ctx->tp > 1 && bs > 1 && ctx->nccl_comm && ctx->opt_tp_batch) {
         // tensor parallel batch (prefill chunk / verify batch): row-sharded GEMMs, one all-gather per exchange for the whole chunk
         if (lm_head && !ctx->tp_logl) { int rc2 = dev_alloc(ctx, (void **)&ctx->tp_logl, (size_t)ctx->d.max_batch * ctx->vocab_l * 4); if (rc2) return rc2; }
@@ -2319,7 +2337,12 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
 // runs per column over its own session's cache.  A session's logits are bit-identical to decoding it alone with batch 1.
 static int refresh_kv_tables(ps_cuda_ctx *ctx) {
     const ps_cuda_model_desc &d = ctx->d;
-    if (ctx->arch) return 0; // the executor takes the active set's pointers with every forward pass
+    if (ctx->arch) { // the executor takes the active set's pointers with every forward pass; the captured steps hold the old ones
+        PS_CK(cudaStreamSynchronize(ctx->stream));
+        if (ctx->g_step) { cudaGraphExecDestroy(ctx->g_step); ctx->g_step = nullptr; }
+        if (ctx->g_fwd) { cudaGraphExecDestroy(ctx->g_fwd); ctx->g_fwd = nullptr; }
+        return 0;
+    }
     std::vector<float *> ptrs(2 * (size_t)d.n_layers);
     for (int L = 0; L < d.n_layers; L++) { ptrs[L] = ctx->kc[L]; ptrs[d.n_layers + L] = ctx->vct[L]; }
     PS_CK(cudaMemcpyAsync(ctx->kv_ptrs_dev, ptrs.data(), sizeof(float *) * ptrs.size(), cudaMemcpyHostToDevice, ctx->stream));
@@ -2566,7 +2589,7 @@ int ps_cuda_decode_greedy(ps_cuda_ctx *ctx, int32_t first_token, int n_steps, in
     ctx->h_tokens[0] = first_token;
     PS_CK(cudaMemcpyAsync(ctx->tokens_dev, ctx->h_tokens, 4, cudaMemcpyHostToDevice, ctx->stream));
     ctx->h2d += 4;
-    if (!ctx->arch && ((ctx->opt_fused && ctx->fused_ok) || ops_graph_usable(ctx) || mv_usable(ctx))) {
+    if (arch_graph_usable(ctx) || (!ctx->arch && ((ctx->opt_fused && ctx->fused_ok) || ops_graph_usable(ctx) || mv_usable(ctx)))) {
         int32_t *slot = &ctx->h_ids[4096];
         slot[0] = ctx->position;
         slot[1] = 0;

@@ -211,7 +211,31 @@ def test_single_token_kernels_match_the_tiled_ones(tmp_path):
         b = run(m, toks, [1])
         # same operands, same roundings: only the summation order differs (in bfloat16 mode a last-bit difference of an fp32
         # activation now and then lands on the other side of a bfloat16 rounding)
-        assert rel_err(a, b).max() < (2e-6 if dtype == "float32" else 1e-3), dtype
+        assert rel_err(a, b).max() < (1e-5 if dtype == "float32" else 1e-3), dtype
+        m.close()
+
+
+def test_replayed_step_matches_the_plain_launches(tmp_path):
+    """token-by-token decoding through the captured-and-replayed step (the default) against the same kernels launched one by one"""
+    d, cfg, t = make(tmp_path, MIXED, width=72, vocab=130, seed=15, rel_rows=10)
+    toks = tokens(130, 90, 15)
+    for dtype in ("float32", "bfloat16"):
+        m = arch.load_model(d, dtype=dtype, max_batch=40, n_ctx=96)
+        g0 = m.be.counter("graph_replays")
+        a = run(m, toks, [1])
+        assert m.be.counter("graph_replays") - g0 == len(toks)
+        m.reset()
+        m.forward(toks[:40], lm_head=False)
+        ids_a = list(m.decode_greedy(toks[40], 20))
+        m.be.set_option("graph", 0)
+        g1 = m.be.counter("graph_replays")
+        b = run(m, toks, [1])
+        assert m.be.counter("graph_replays") == g1
+        m.reset()
+        m.forward(toks[:40], lm_head=False)
+        ids_b = list(m.decode_greedy(toks[40], 20))
+        np.testing.assert_array_equal(a, b)             # the same kernels on the same data
+        assert ids_a == ids_b
         m.close()
 
 
@@ -230,7 +254,9 @@ def test_tensor_core_gemm_matches_the_tile_kernels(tmp_path):
     n2 = m.be.counter("kernel_launches")
     assert n1 - n0 > n2 - n1                                    # the tensor-core path adds its operand-tiling launches: it did run
     e = rel_err(a, b)
-    assert np.median(e) < 2e-4 and (e > 2e-3).sum() <= 3, (np.median(e), e.max())
+    # same operands, another summation order: an fp32 activation that differs in its last bit now and then lands on the other side of
+    # a bfloat16 rounding (one operand off by 2^-8 of itself), which shows as 1e-3 at that position; a wrong tile would show as O(1)
+    assert np.median(e) < 1e-5 and np.quantile(e, 0.9) < 2e-3 and e.max() < 8e-3, (np.median(e), e.max())
     check(a, R.forward(cfg, t, toks), "bfloat16", "tensor-core path against the oracle")
     m.close()
 
