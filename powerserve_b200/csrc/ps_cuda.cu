@@ -1957,7 +1957,7 @@ int ps_cuda_bind_model(ps_cuda_ctx *ctx, const ps_cuda_model_weights *w) {
 // token positions are, and the attention bias is ctx->tree_bias (slot mask + in-batch tree mask) instead of the causal `pos` mask.
 struct SessRun { int n_kv_max; };
 // Scores and P.V of a batch over one cache (prefill chunk, verify batch): register-tiled kernels (option attn_tile, on
-// by default), else the round-1 kernels; narrow batches use the per-position / per-(head, dim) warp kernels.  nh / nkv
+// by default), else the first-generation kernels; narrow batches use the per-position / per-(head, dim) warp kernels.  nh / nkv
 // are the heads THIS rank owns.  The caller checks the launch (PS_LAUNCH_CK) after launch_batch_scores.
 static void launch_batch_scores(ps_cuda_ctx *ctx, int L, int nh, int nkv, int hs, int64_t n_kv, int bs) {
     if (bs >= ctx->opt_scores_batch_min) {
@@ -2787,7 +2787,7 @@ int ps_cuda_set_option(ps_cuda_ctx *ctx, const char *name, int value) {
     else if (!strcmp(name, "rwm_tile")) ctx->opt_rwm_tile = value;       // 1 (default): the multi-column row-walker shrinks its row tile so that narrow batches use every SM; 0: 16-octet tiles
     else if (!strcmp(name, "scores_batch_min")) ctx->opt_scores_batch_min = std::max(1, value); // batches at least this wide use the query-blocked scores kernel
     else if (!strcmp(name, "tc_min")) ctx->opt_tc_min = std::max(2, value); // narrowest batch that takes the tcgen05 GEMM (narrower ones: multi-column row-walker)
-    else if (!strcmp(name, "attn_tile")) ctx->opt_attn_tile = value; // register-tiled scores / P.V kernels for batches (0: the round-1 kernels, for A/B)
+    else if (!strcmp(name, "attn_tile")) ctx->opt_attn_tile = value; // register-tiled scores / P.V kernels for batches (0: the first-generation kernels, for A/B)
     else if (!strcmp(name, "pv_batch_min")) ctx->opt_pv_batch_min = value; // batches at least this wide use the query-blocked P.V kernel (prefill), narrower ones the per-(head, dim) warp kernel
     else if (!strcmp(name, "rw_unroll2")) ctx->opt_unroll2 = value; // tuning: two blocks per loop trip in the mat-vec launches with <= 8 octets per CTA
     else if (!strcmp(name, "attn_group")) ctx->opt_attn_group = value; // 1: decode attention as one group-synchronised kernel per layer (bit-exact, slower so far: DESIGN.md 5b); 0 (default): scores kernel + soft-max / P.V kernel

@@ -3,7 +3,7 @@
 // 148 resident CTAs that walk the phases of every layer together.  Same arithmetic as the per-phase kernels in ps_rw.cuh /
 // ps_decode.cuh (block math, FMA chains, quantiser, soft-max: all shared device functions), bit-identical to the table ops.
 //
-// Why (round-1 measurements): the per-phase kernels stream their weights at 5.6-6.0 TB/s once they
+// Why (measured): the per-phase kernels stream their weights at 5.6-6.0 TB/s once they
 // run, but a decode step was 62 % fixed cost - six kernel boundaries per layer, each with ~1 us of dependency latency
 // and a 2-5 us prologue during which DRAM idles, because a CTA that holds 200 KB of shared memory cannot overlap with
 // its successor.  Here the weight stream never stops:

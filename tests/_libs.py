@@ -1,4 +1,4 @@
-"""ctypes loaders for the CHECKERS used by the tests: oracle/libps_oracle.so (our restatement) and, when present,
+"""ctypes loaders for the ORACLES used by the tests: oracle/libps_oracle.so (our restatement) and, when present,
 oracle/_ref/*.so (the reference compiled from /root/reference).  Test infrastructure only."""
 from __future__ import annotations
 

@@ -1,4 +1,4 @@
-"""GPU tests of the C-ABI entries the round-1 suite did not touch: ps_cuda_copy_2d (the `copy` / `cont` twin), the KV
+"""GPU tests of the C-ABI entries the first suite did not touch: ps_cuda_copy_2d (the `copy` / `cont` twin), the KV
 position bookkeeping (truncate / advance / rollback, kv_cache.hpp:97-163 semantics), the exposed cache pointers
 (ps_cuda_kv_k / ps_cuda_kv_v against the oracle's cache contents) and ps_cuda_logits_dev."""
 import numpy as np

@@ -72,7 +72,7 @@ def test_tiled_batch_attention_ragged_shapes(preset, n_prompt, batch):
     """The register-tiled scores / P.V kernels (reduce-scatter reductions, permuted cache rows, 8 x 8 accumulator tiles)
     on shapes that hit every edge: query blocks that are not full (batch % 8), cache lengths with leftovers (n_kv % 32),
     fewer than 32 cached positions, head sizes 64 / 128, 3 / 4 / 7 query heads per kv head.  Bit-equal to the oracle and
-    to the round-1 kernels (option attn_tile = 0)."""
+    to the first-generation kernels (option attn_tile = 0)."""
     d = M.model_dir(preset)
     shape = synth.PRESETS[preset]
     prompt = synth.random_prompt(shape.vocab_size, n_prompt, seed=11 + n_prompt)
@@ -86,14 +86,14 @@ def test_tiled_batch_attention_ragged_shapes(preset, n_prompt, batch):
     cm.reset()
     cm.be.set_option("attn_tile", 0)
     ids_b, lg_b = cm.generate(prompt, 4, batch_size=batch)
-    L.assert_bit_equal(lg_b, lg_c, f"{preset} logits, round-1 batch attention kernels")
+    L.assert_bit_equal(lg_b, lg_c, f"{preset} logits, first-generation batch attention kernels")
     cm.close()
 
 
 @pytest.mark.parametrize("preset", ["tiny-hs32", "tiny-hs96", "tiny-hs256"])
 def test_head_sizes_off_the_templated_paths(preset):
     """Head sizes 32 / 96 / 256: the decode scores kernel's generic step loop (ST = 8 template), the head-size-templated
-    batch scores kernel for 32 and 256, the round-1 batch kernels for 96.  Prefill in chunks, host-driven decode and the
+    batch scores kernel for 32 and 256, the first-generation batch kernels for 96.  Prefill in chunks, host-driven decode and the
     device-resident greedy loop, bit-equal to the oracle."""
     d = M.model_dir(preset)
     shape = synth.PRESETS[preset]
