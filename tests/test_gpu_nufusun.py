@@ -396,3 +396,27 @@ def test_trace_runner_replays_steps(tmp_path):
         check(np.fromfile(out / "3.f32", "<f4").reshape(1, 130), rb[[16]], dtype, "step 3")
         for f in out.iterdir():
             f.unlink()
+
+
+def test_generation_command_line(tmp_path):
+    """bin/ps_generate on a layer-list directory: greedy ids equal the model's own generate(); top-k sampling stays inside the k best"""
+    d, cfg, t = make(tmp_path, MIXED, width=72, vocab=130, seed=16, rel_rows=10)
+    prompt = tokens(130, 19, 16)
+    exe = os.path.join(ROOT, "bin", "ps_generate")
+    p = subprocess.run([exe, "--model", d, "--dtype", "float32", "--ids", " ".join(map(str, prompt)), "--n", "10", "--prefill-batch", "8"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    ids = json.loads(p.stdout.strip().splitlines()[-1])["ids"]
+    m = arch.load_model(d, dtype="float32", max_batch=32, n_ctx=32)
+    want, _ = m.generate(prompt, 10, batch_size=8)
+    assert ids == want
+    p = subprocess.run([exe, "--model", d, "--dtype", "float32", "--ids", ",".join(map(str, prompt)), "--n", "6", "--top-k", "3", "--seed", "5"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    sampled = json.loads(p.stdout.strip().splitlines()[-1])["ids"]
+    seq = list(prompt)
+    for tok in sampled:
+        m.reset()
+        lg = m.forward(seq)[-1]
+        assert tok in np.argsort(-lg, kind="stable")[:3]
+        seq.append(tok)
+    m.close()
+    assert subprocess.run([exe, "--model", d, "--ids", "", "--n", "3"], capture_output=True, text=True, timeout=600).returncode == 2
