@@ -46,6 +46,8 @@ struct PsArch {
     float *y = nullptr, *slot = nullptr, *sel_w = nullptr, *row_w = nullptr;
     int *sel_e = nullptr, *row_token = nullptr, *row_slot = nullptr, *tile_e = nullptr, *tile_row0 = nullptr, *tile_end = nullptr, *n_tiles = nullptr;
     float *z = nullptr;    // router logits of the single-token step
+    float *pm = nullptr, *pl = nullptr; // per-block soft-max statistics of the single-token step
+    int ldP = 0;
     int64_t ldS = 0;
     int max_qkv = 0, max_od = 0, max_h = 0, max_top = 0, max_ff = 0, max_e = 0, max_dv = 0;
     int taps_on = 0;
@@ -55,6 +57,10 @@ struct PsArch {
     int opt_tc = 1;     // bfloat16 batches (bs >= 2) run on the tcgen05 GEMM; 0 = the fp32-FMA tile kernels on rounded operands
     int opt_simple = 0; // 1: every batch width takes the tiled kernels (the single-token kernels are skipped; tests compare the two)
     int n_sm = 148;
+    // single-token step: the experts' gate | up product needs only the router logits, so it runs beside the attention kernels
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    int opt_fork = 1;
 };
 
 namespace {
@@ -230,6 +236,9 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     AL(a->tile_end, 4 * ntile);
     AL(a->n_tiles, 16);
     AL(a->z, 4 * (size_t)std::max(a->max_e, 1));
+    a->ldP = (d.n_ctx + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    AL(a->pm, 4 * (size_t)a->max_h * a->ldP);
+    AL(a->pl, 4 * (size_t)a->max_h * a->ldP);
     if (rc) return bail(rc);
     int dev = 0;
     cudaGetDevice(&dev);
@@ -245,12 +254,20 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         cudaGetLastError();
         return bail(afail(err, PS_CUDA_ERR_CUDA, "cudaFuncSetAttribute(dynamic shared memory) failed"));
     }
+    if (cudaStreamCreateWithFlags(&a->side, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreateWithFlags(&a->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&a->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return bail(afail(err, PS_CUDA_ERR_CUDA, "side stream / events of the single-token step could not be created"));
+    }
     *out = a;
     return 0;
 }
 
 void ps_arch_destroy(PsArch *a) {
     if (!a) return;
+    if (a->ev_fork) cudaEventDestroy(a->ev_fork);
+    if (a->ev_join) cudaEventDestroy(a->ev_join);
+    if (a->side) cudaStreamDestroy(a->side);
     for (void *p : a->owned) cudaFree(p);
     delete a;
 }
@@ -265,6 +282,7 @@ int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
     if (!strcmp(name, "arch_tc")) { a->opt_tc = value; return 1; }
+    if (!strcmp(name, "arch_fork")) { a->opt_fork = value; return 1; }
     return 0;
 }
 
@@ -371,6 +389,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         while (ks < 8 && (rows + 16 / ks - 1) / (16 / ks) < 4 * a->n_sm && K % (16 * ks) == 0 && K / (2 * ks) >= 256) ks *= 2;
         return ks;
     };
+    // the mat-vec CTAs walk the row groups with the grid's stride: at most four resident CTAs per SM, one wave
+    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)(4 * a->n_sm)); };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
     auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
@@ -402,7 +422,18 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.qd = w.qd; mv.kd = w.kd; mv.vd = w.vd; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
             if (routed) { mv.Wr = w.router; mv.E = l.n_experts; mv.z = a->z; }
             mv.ksplit = pick_ksplit(nqkv + mv.E, dim);
-            pa_k_dec_mv<ROUND><<<cdiv(nqkv + mv.E, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
+            pa_k_dec_mv<ROUND><<<mv_grid(nqkv + mv.E, mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
+            if (routed) {
+                // gate | up of the chosen experts: reads x and the router logits only, so it runs on the side stream while the main
+                // stream goes through scores, P.V and the output projection (a fork in the captured graph); joined before `down`
+                PA_LAUNCH();
+                cudaStream_t se = a->opt_fork ? a->side : st;
+                if (a->opt_fork) { PA_CK(cudaEventRecord(a->ev_fork, st)); PA_CK(cudaStreamWaitEvent(se, a->ev_fork, 0)); }
+                pa_k_dec_expert_up<ROUND><<<dim3(std::min(cdiv(l.expert_ff, PA_DV_ROWS / 2), (unsigned)std::max(1, 4 * a->n_sm / l.top_k)), l.top_k), PA_DV_THREADS, 4 * (size_t)dim, se>>>(
+                    a->x, w.norm, d.norm_eps, a->z, l.n_experts, l.top_k, l.route_renorm, w.wgate, w.wup, a->y, l.expert_ff, dim, l.route_on_input, l.act_limit, l.act_alpha,
+                    l.up_shift, a->sel_e, a->sel_w);
+                if (a->opt_fork) PA_CK(cudaEventRecord(a->ev_join, se));
+            }
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, w.t_qkv, nqkv, w.bqkv, a->qkv, nqkv);
             if (rc) return rc;
@@ -416,7 +447,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         }
         PaAttn at;
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
-        at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B;
+        at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
         if (single) {
             pa_k_dec_scores<<<cdiv(n_kv_cap, PA_DS_KEYS), 256, pa_dec_scores_smem(H, G, dq), st>>>(at, a->qkv, io.kc[li], io.pos_dev, a->S, io.err_dev);
             PA_LAUNCH();
@@ -435,7 +466,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.x = a->att; mv.W = w.wo; mv.bias = w.bo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
             if (!routed) mv.residual = a->x; // no feed-forward: the layer ends here
             mv.ksplit = pick_ksplit(dim, w.od);
-            pa_k_dec_mv<ROUND><<<cdiv(dim, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 0, st>>>(mv);
+            pa_k_dec_mv<ROUND><<<mv_grid(dim, mv.ksplit), PA_DV_THREADS, 0, st>>>(mv);
         } else if (tc) {
             int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
             if (rc) return rc;
@@ -453,10 +484,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 PA_LAUNCH();
             }
             if (single) {
-                (void)n;
-                pa_k_dec_expert_up<ROUND><<<dim3(cdiv(ff, PA_DV_ROWS / 2), top), PA_DV_THREADS, 4 * (size_t)dim, st>>>(
-                    a->x, w.norm, d.norm_eps, a->z, E, top, l.route_renorm, w.wgate, w.wup, a->y, ff, dim, l.route_on_input, l.act_limit, l.act_alpha, l.up_shift, a->sel_e, a->sel_w);
-                PA_LAUNCH();
+                (void)n; (void)E;
+                if (a->opt_fork) PA_CK(cudaStreamWaitEvent(st, a->ev_join, 0));
                 const int ksd = pick_ksplit(dim, ff);
                 pa_k_dec_expert_down<ROUND><<<cdiv(dim, PA_DV_ROWS / ksd), PA_DV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, top, w.wdown, a->ao, a->x, dim, ff, l.route_on_input, ksd);
                 PA_LAUNCH();
@@ -511,7 +540,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             PaMv mv{};
             mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
             mv.ksplit = pick_ksplit(d.vocab_size, dim);
-            pa_k_dec_mv<ROUND><<<cdiv(d.vocab_size, PA_DV_ROWS / mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
+            pa_k_dec_mv<ROUND><<<mv_grid(d.vocab_size, mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);
             if (rc) return rc;

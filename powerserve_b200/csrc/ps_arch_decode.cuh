@@ -25,7 +25,7 @@ __device__ __forceinline__ void pa_dot2(const bf16 *__restrict__ w0, const bf16 
     s0 = s1 = 0.f;
     if (k_end < 0) k_end = K;
     if ((K & 7) == 0 && (k_begin & 7) == 0) {
-#pragma unroll 2
+#pragma unroll 4
         for (int k = k_begin + lane * 8; k < k_end; k += 256) {
             const uint4 a = __ldg(reinterpret_cast<const uint4 *>(w0 + k));
             const uint4 b = __ldg(reinterpret_cast<const uint4 *>(w1 + k));
@@ -109,55 +109,64 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int ks = a.ksplit, pairs = 8 / ks, pair = warp % pairs, slice = warp / pairs;
     const int total = a.N + a.E;
-    const int n0 = (blockIdx.x * pairs + pair) * 2, n1 = min(n0 + 1, total - 1);
+    const int groups = (total + 2 * pairs - 1) / (2 * pairs); // row groups of `pairs` row pairs; the CTAs walk them with the grid's stride
     const int kc = a.K / ks, k_begin = slice * kc, k_end = slice == ks - 1 ? a.K : k_begin + kc;
-    const bool live = n0 < total;
-    // rows of the pair: weight rows below N, router rows (fp32 input, never rounded) from N on
-    const bf16 *w0 = nullptr, *w1 = nullptr;
-    if (live) {
-        w0 = n0 < a.N ? a.W + (int64_t)n0 * a.K : a.Wr + (int64_t)(n0 - a.N) * a.K;
-        w1 = n1 < a.N ? a.W + (int64_t)n1 * a.K : a.Wr + (int64_t)(n1 - a.N) * a.K;
-        pa_prefetch2(w0, w1, k_begin, k_end, lane);
-    }
+    // rows of a pair: weight rows below N, router rows (fp32 input, never rounded) from N on
+    auto row = [&](int n) { return n < a.N ? a.W + (int64_t)n * a.K : a.Wr + (int64_t)(n - a.N) * a.K; };
+    auto prefetch = [&](int grp) {
+        const int n0 = (grp * pairs + pair) * 2;
+        if (n0 < total) pa_prefetch2(row(n0), row(min(n0 + 1, total - 1)), k_begin, k_end, lane);
+    };
+    prefetch(blockIdx.x);
     const float *xin = a.x;
     if (a.norm_w) {
         pa_norm_to_smem(pa_hs, a.x, a.norm_w, a.K, a.eps);
         xin = pa_hs;
     }
-    float s0 = 0.f, s1 = 0.f;
-    if (live) {
-        if (n0 >= a.N) {
-            pa_dot2<false>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
-        } else if (n1 >= a.N) { // the pair straddles the two matrices
-            float t;
-            pa_dot2<ROUND>(w0, w0, xin, a.K, 1.0f, lane, s0, t, k_begin, k_end);
-            pa_dot2<false>(w1, w1, xin, a.K, 1.0f, lane, s1, t, k_begin, k_end);
-        } else {
-            pa_dot2<ROUND>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
+    for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+        if (grp + (int)gridDim.x < groups) prefetch(grp + gridDim.x); // the next group's rows travel to L2 while this one is summed
+        const int n0 = (grp * pairs + pair) * 2, n1 = min(n0 + 1, total - 1);
+        const bool live = n0 < total;
+        float s0 = 0.f, s1 = 0.f;
+        if (live) {
+            const bf16 *w0 = row(n0), *w1 = row(n1);
+            if (n0 >= a.N) {
+                pa_dot2<false>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
+            } else if (n1 >= a.N) { // the pair straddles the two matrices
+                float t;
+                pa_dot2<ROUND>(w0, w0, xin, a.K, 1.0f, lane, s0, t, k_begin, k_end);
+                pa_dot2<false>(w1, w1, xin, a.K, 1.0f, lane, s1, t, k_begin, k_end);
+            } else {
+                pa_dot2<ROUND>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
+            }
         }
-    }
-    if (ks > 1) {
-        if (lane == 0) { part_s[warp][0] = s0; part_s[warp][1] = s1; }
-        __syncthreads();
-        if (slice != 0) return;
-        s0 = s1 = 0.f;
-        for (int q = 0; q < ks; q++) { s0 += part_s[q * pairs + pair][0]; s1 += part_s[q * pairs + pair][1]; }
-    }
-    if (live && lane < 2) {
-        const int n = lane ? n1 : n0;
-        if (lane && n1 == n0) return;
-        float v = lane ? s1 : s0;
-        if (n >= a.N) { a.z[n - a.N] = v; return; }
-        if (a.bias) v += a.bias[n];
-        if (a.kd && n >= a.qd) {
-            const int p = a.pos[0];
-            if (n < a.qd + a.kd) a.kc[(int64_t)p * a.kd + (n - a.qd)] = v;
-            else a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
-        } else if (a.residual) {
-            a.residual[n] += v;
-        } else {
-            a.y[n] = v;
+        if (ks > 1) {
+            if (lane == 0) { part_s[warp][0] = s0; part_s[warp][1] = s1; }
+            __syncthreads();
+            if (slice == 0) {
+                s0 = s1 = 0.f;
+                for (int q = 0; q < ks; q++) { s0 += part_s[q * pairs + pair][0]; s1 += part_s[q * pairs + pair][1]; }
+            }
         }
+        if (slice == 0 && live && lane < 2 && !(lane && n1 == n0)) {
+            const int n = lane ? n1 : n0;
+            float v = lane ? s1 : s0;
+            if (n >= a.N) {
+                a.z[n - a.N] = v;
+            } else {
+                if (a.bias) v += a.bias[n];
+                if (a.kd && n >= a.qd) {
+                    const int p = a.pos[0];
+                    if (n < a.qd + a.kd) a.kc[(int64_t)p * a.kd + (n - a.qd)] = v;
+                    else a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
+                } else if (a.residual) {
+                    a.residual[n] += v;
+                } else {
+                    a.y[n] = v;
+                }
+            }
+        }
+        if (ks > 1) __syncthreads(); // part_s is written again by the next group
     }
 }
 
@@ -211,33 +220,52 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
                 if (lane == 0) {
 #pragma unroll
                     for (int r = 0; r < 4; r++)
-                        if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = pa_score(at, s[r], g * rep + r0 + r, pos - (j0 + jj));
+                        if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = s[r];
                 }
             }
         }
     }
     __syncthreads();
-    for (int t = tid; t < nj * H; t += 256) {
-        const int h = t / nj, jj = t % nj; // jj fastest: the stores of a head are contiguous
-        float s;
-        if (at.mix) {
-            s = 0.f;
-            for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
-        } else {
-            s = sa[jj * H + h];
+    // scale / temperature / distance bias for every (key, head) at once: the table look-ups are dependent global loads
+    for (int t = tid; t < nj * H; t += 256) sa[t] = pa_score(at, sa[t], t % H, pos - (j0 + t / H));
+    __syncthreads();
+    // mix the heads, store, and leave the block's soft-max statistics (max, sum of exponentials) for the P.V kernel:
+    // the 16 keys of a head sit in 16 adjacent lanes
+    const int n_t = (PA_DS_KEYS * H + 31) & ~31;
+    for (int t = tid; t < n_t; t += 256) {
+        const int h = t / PA_DS_KEYS, jj = t % PA_DS_KEYS;
+        const bool valid = h < H && jj < nj;
+        float s = -INFINITY;
+        if (valid) {
+            if (at.mix) {
+                s = 0.f;
+                for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
+            } else {
+                s = sa[jj * H + h];
+            }
+            b[(int64_t)h * at.ldS + j0 + jj] = s;
         }
-        b[(int64_t)h * at.ldS + j0 + jj] = s;
+        float m = s;
+#pragma unroll
+        for (int o = PA_DS_KEYS / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float e = valid ? expf(s - m) : 0.f;
+#pragma unroll
+        for (int o = PA_DS_KEYS / 2; o; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
+        if (valid && jj == 0) {
+            at.pm[(int64_t)h * at.ldP + blockIdx.x] = m;
+            at.pl[(int64_t)h * at.ldP + blockIdx.x] = e;
+        }
     }
 }
 
 // att[h][c] = sum_j p_hj V^T[g(h) dv + c][j] for one kv head g and PA_DP_DIMS value dims; p = soft-max of b[h][0 .. pos] with the
-// optional sink term.  Phase 1: max and sum of every query head of the group.  Phase 2, per chunk of keys: the CTA's V^T rows
+// optional sink term.  Phase 1: max and sum of every query head of the group, merged from the per-block pairs the scores kernel
+// left (16 keys each).  Phase 2, per chunk of keys: the CTA's V^T rows
 // arrive by 1-D bulk copies while the threads compute the chunk's weights once into shared memory; two warps per value dim
 // (the halves of the chunk) then run float4 dot products out of shared memory for every head of the group.
 __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__restrict__ b, const float *__restrict__ vct, const int32_t *__restrict__ pos_dev,
                                                    float *__restrict__ att, int chunk, int *__restrict__ err) {
     extern __shared__ __align__(16) float sm[];
-    __shared__ float red[8];
     __shared__ __align__(8) uint64_t bar;
     const int H = at.H, G = at.G, dv = at.dv, rep = H / G, g = blockIdx.y;
     float *vs = sm;                         // [PA_DP_DIMS][chunk] V^T rows of the chunk
@@ -253,31 +281,23 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
         ps_fence_barrier_init();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int r = 0; r < rep; r++) {
-        const float *row = b + (int64_t)(g * rep + r) * at.ldS;
+    // soft-max statistics of every head of the group from the scores kernel's per-block pairs: a warp per head
+    const int nb = (n + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    for (int r = warp; r < rep; r += 8) {
+        const float *bm = at.pm + (int64_t)(g * rep + r) * at.ldP, *bl = at.pl + (int64_t)(g * rep + r) * at.ldP;
         float mx = at.sink ? 0.f : -INFINITY;
-        for (int j = tid; j < n; j += 256) mx = fmaxf(mx, row[j]);
+        for (int j = lane; j < nb; j += 32) mx = fmaxf(mx, bm[j]);
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red[warp] = mx;
-        __syncthreads();
-        mx = red[0];
-        for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w]);
-        __syncthreads();
         float sum = 0.f;
-        for (int j = tid; j < n; j += 256) sum += expf(row[j] - mx);
+        for (int j = lane; j < nb; j += 32) sum = fmaf(bl[j], expf(bm[j] - mx), sum);
 #pragma unroll
         for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) red[warp] = sum;
-        __syncthreads();
-        if (tid == 0) {
-            float t = 0.f;
-            for (int w = 0; w < 8; w++) t += red[w];
-            if (at.sink) t += expf(-mx);
+        if (lane == 0) {
+            if (at.sink) sum += expf(-mx);
             ms[r] = mx;
-            inv[r] = 1.0f / t;
+            inv[r] = 1.0f / sum;
         }
-        __syncthreads();
     }
     for (int t = tid; t < 8 * rep; t += 256) acc[t] = 0.f;
     const int dim_l = warp % PA_DP_DIMS, part = warp / PA_DP_DIMS, n_part = 8 / PA_DP_DIMS;
@@ -367,12 +387,16 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
     pa_norm_to_smem(pa_hs, x, norm_w, dim, eps); // (its barriers also publish se / sw)
     const int r = blockIdx.y, e = se[r], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float w = on_input ? sw[r] : 1.0f;
-    // a warp owns one ff row: its gate row and its up row are the pair
-    const int n = blockIdx.x * (PA_DV_ROWS / 2) + warp;
-    if (n >= ff) return;
-    float gsum, usum;
-    pa_dot2<ROUND>(Wg + ((int64_t)e * ff + n) * dim, Wu + ((int64_t)e * ff + n) * dim, pa_hs, dim, w, lane, gsum, usum);
-    if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+    // a warp owns one ff row at a time: its gate row and its up row are the pair; the CTAs walk the row groups with the grid's stride
+    const int rows = PA_DV_ROWS / 2;
+    for (int n = blockIdx.x * rows + warp; n < ff; n += gridDim.x * rows) {
+        const bf16 *wg = Wg + ((int64_t)e * ff + n) * dim, *wu = Wu + ((int64_t)e * ff + n) * dim;
+        const int nn = n + gridDim.x * rows;
+        if (nn < ff) pa_prefetch2(wg + (int64_t)gridDim.x * rows * dim, wu + (int64_t)gridDim.x * rows * dim, 0, dim, lane);
+        float gsum, usum;
+        pa_dot2<ROUND>(wg, wu, pa_hs, dim, w, lane, gsum, usum);
+        if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+    }
 }
 
 // x[n] += ao[n] + sum_r down_{e_r}[n] . round(y_r)  (times w_r when the score weighs the output); slots in order; `ksplit`

@@ -24,6 +24,8 @@ struct PaAttn {
     int n_ctx;
     int64_t ldS;            // row stride of the score rows
     int B;                  // rows per head in the score buffer (max_batch)
+    float *pm, *pl;         // single-token step: per head and block of keys, max and sum of exponentials of the mixed scores
+    int ldP;                // blocks per head in pm / pl
 };
 
 template <bool ROUND> __device__ __forceinline__ float pa_rnd(float v) {

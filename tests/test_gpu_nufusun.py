@@ -236,6 +236,10 @@ def test_replayed_step_matches_the_plain_launches(tmp_path):
         ids_b = list(m.decode_greedy(toks[40], 20))
         np.testing.assert_array_equal(a, b)             # the same kernels on the same data
         assert ids_a == ids_b
+        m.be.set_option("arch_fork", 0)                 # gate | up of the experts behind the attention instead of beside it
+        np.testing.assert_array_equal(run(m, toks, [1]), a)
+        m.be.set_option("graph", 1)
+        np.testing.assert_array_equal(run(m, toks, [1]), a)
         m.close()
 
 
