@@ -61,6 +61,7 @@ struct PsArch {
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int opt_fork = 1;
+    int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
 };
 
 namespace {
@@ -158,6 +159,23 @@ int pa_dec_pv_chunk(int H, int G) { return std::max(32, (PA_DP_FLOATS / (PA_DP_D
 size_t pa_dec_pv_smem(int H, int G) {
     const int rep = H / G;
     return 4 * ((size_t)(PA_DP_DIMS + rep) * pa_dec_pv_chunk(H, G) + (size_t)(2 + 8) * rep);
+}
+
+// a launch that may overlap the end of the kernel before it in the stream (the kernel calls griddepcontrol.wait before it reads
+// anything that kernel wrote)
+template <typename... KArgs, typename... Args>
+cudaError_t pa_launch_dep(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
 } // namespace
@@ -283,6 +301,7 @@ int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
     if (!strcmp(name, "arch_tc")) { a->opt_tc = value; return 1; }
     if (!strcmp(name, "arch_fork")) { a->opt_fork = value; return 1; }
+    if (!strcmp(name, "arch_pdl")) { a->opt_pdl = value; return 1; }
     return 0;
 }
 
@@ -390,7 +409,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return ks;
     };
     // the mat-vec CTAs walk the row groups with the grid's stride: at most four resident CTAs per SM, one wave
-    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)(4 * a->n_sm)); };
+    // (two per SM when the launches overlap: the next kernel's CTAs need room beside them to fetch their weights early)
+    const bool pdl = a->opt_pdl != 0;
+    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)((pdl ? 2 : 4) * a->n_sm)); };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
     auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
@@ -422,7 +443,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.qd = w.qd; mv.kd = w.kd; mv.vd = w.vd; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
             if (routed) { mv.Wr = w.router; mv.E = l.n_experts; mv.z = a->z; }
             mv.ksplit = pick_ksplit(nqkv + mv.E, dim);
-            pa_k_dec_mv<ROUND><<<mv_grid(nqkv + mv.E, mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(nqkv + mv.E, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
             if (routed) {
                 // gate | up of the chosen experts: reads x and the router logits only, so it runs on the side stream while the main
                 // stream goes through scores, P.V and the output projection (a fork in the captured graph); joined before `down`
@@ -449,9 +470,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
         at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
         if (single) {
-            pa_k_dec_scores<<<cdiv(n_kv_cap, PA_DS_KEYS), 256, pa_dec_scores_smem(H, G, dq), st>>>(at, a->qkv, io.kc[li], io.pos_dev, a->S, io.err_dev);
+            pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
             PA_LAUNCH();
-            pa_k_dec_pv<<<dim3(cdiv(dv, PA_DP_DIMS), G), 256, pa_dec_pv_smem(H, G), st>>>(at, a->S, io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
+            pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();
         } else {
             pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs);
@@ -466,7 +487,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.x = a->att; mv.W = w.wo; mv.bias = w.bo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
             if (!routed) mv.residual = a->x; // no feed-forward: the layer ends here
             mv.ksplit = pick_ksplit(dim, w.od);
-            pa_k_dec_mv<ROUND><<<mv_grid(dim, mv.ksplit), PA_DV_THREADS, 0, st>>>(mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(dim, mv.ksplit)), dim3(PA_DV_THREADS), 0, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
             if (rc) return rc;
@@ -540,7 +561,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             PaMv mv{};
             mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
             mv.ksplit = pick_ksplit(d.vocab_size, dim);
-            pa_k_dec_mv<ROUND><<<mv_grid(d.vocab_size, mv.ksplit), PA_DV_THREADS, 4 * (size_t)dim, st>>>(mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(d.vocab_size, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);
             if (rc) return rc;

@@ -118,6 +118,9 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
         if (n0 < total) pa_prefetch2(row(n0), row(min(n0 + 1, total - 1)), k_begin, k_end, lane);
     };
     prefetch(blockIdx.x);
+    // launched with programmatic stream serialisation: everything above touches weights only and overlaps the kernel before
+    ps_grid_dep_launch();
+    ps_grid_dep_wait();
     const float *xin = a.x;
     if (a.norm_w) {
         pa_norm_to_smem(pa_hs, a.x, a.norm_w, a.K, a.eps);
@@ -184,6 +187,9 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     float *sa = qs + H * dq;               // [PA_DS_KEYS][H]
     float *Ts = sa + PA_DS_KEYS * H;       // [H][H]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t]; // a weight: fetched before the dependency wait
+    ps_grid_dep_launch();
+    ps_grid_dep_wait();
     const int pos = pos_dev[0], j0 = blockIdx.x * PA_DS_KEYS;
     if (j0 > pos) return;
     const int nj = min(PA_DS_KEYS, pos + 1 - j0);
@@ -197,7 +203,6 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     }
     if (!bulk) for (int t = tid; t < nj * kd; t += 256) ks[t] = kc[(int64_t)j0 * kd + t];
     for (int t = tid; t < H * dq; t += 256) qs[t] = q[t];
-    if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t];
     __syncthreads();
     if (bulk && !ps_tc_wait(&bar, 0)) { if (tid == 0) err[0] = 5; return; }
     for (int jj = warp; jj < nj; jj += 8) {
@@ -274,6 +279,8 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     float *inv = ms + rep;                  // [rep] 1 / denominators
     float *acc = inv + rep;                 // [8 warps][rep]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    ps_grid_dep_launch();
+    ps_grid_dep_wait();
     const int n = pos_dev[0] + 1;
     const bool bulk = (at.n_ctx & 3) == 0;
     if (bulk && tid == 0) {
@@ -406,6 +413,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_down(const floa
                                                                       const bf16 *__restrict__ Wd, const float *__restrict__ ao, float *__restrict__ x, int dim, int ff,
                                                                       int on_input, int ksplit) {
     __shared__ float part_s[8][2];
+    ps_grid_dep_launch(); // the next kernel (the next layer's q|k|v rows, or the head) may start fetching its weights
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pairs = 8 / ksplit, pair = warp % pairs, slice = warp / pairs;
     const int n0 = (blockIdx.x * pairs + pair) * 2, n1 = min(n0 + 1, dim - 1);

@@ -240,6 +240,8 @@ def test_replayed_step_matches_the_plain_launches(tmp_path):
         np.testing.assert_array_equal(run(m, toks, [1]), a)
         m.be.set_option("graph", 1)
         np.testing.assert_array_equal(run(m, toks, [1]), a)
+        m.be.set_option("arch_pdl", 0)                  # every launch waits for the whole kernel before it
+        np.testing.assert_array_equal(run(m, toks, [1]), a)
         m.close()
 
 
