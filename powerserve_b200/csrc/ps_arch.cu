@@ -61,6 +61,8 @@ struct PsArch {
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int opt_fork = 1;
+    int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, else four)
+    int opt_prefetch = 1; // 1: a mat-vec CTA requests its first row group into L2 before the dependency wait; 2: every next group too
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
 };
 
@@ -154,7 +156,7 @@ void build_bucket_table(int rows, float dmax, int n, std::vector<uint16_t> &t) {
 }
 
 // shared memory of the single-token kernels
-size_t pa_dec_scores_smem(int H, int G, int dq) { return 4 * ((size_t)PA_DS_KEYS * G * dq + (size_t)H * dq + (size_t)PA_DS_KEYS * H + (size_t)H * H); }
+size_t pa_dec_scores_smem(int H, int G, int dq) { return 4 * ((size_t)PA_DS_KEYS * (((G * dq + 3) & ~3) + 4) + (size_t)H * dq + (size_t)(PA_DS_KEYS + 1) * H + (size_t)H * H); }
 int pa_dec_pv_chunk(int H, int G) { return std::max(32, (PA_DP_FLOATS / (PA_DP_DIMS + H / G)) & ~31); }
 size_t pa_dec_pv_smem(int H, int G) {
     const int rep = H / G;
@@ -302,6 +304,8 @@ int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_tc")) { a->opt_tc = value; return 1; }
     if (!strcmp(name, "arch_fork")) { a->opt_fork = value; return 1; }
     if (!strcmp(name, "arch_pdl")) { a->opt_pdl = value; return 1; }
+    if (!strcmp(name, "arch_mv_cap")) { a->opt_mv_cap = value; return 1; }
+    if (!strcmp(name, "arch_prefetch")) { a->opt_prefetch = value; return 1; }
     return 0;
 }
 
@@ -411,7 +415,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     // the mat-vec CTAs walk the row groups with the grid's stride: at most four resident CTAs per SM, one wave
     // (two per SM when the launches overlap: the next kernel's CTAs need room beside them to fetch their weights early)
     const bool pdl = a->opt_pdl != 0;
-    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)((pdl ? 2 : 4) * a->n_sm)); };
+    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)((a->opt_mv_cap > 0 ? a->opt_mv_cap : pdl ? 2 : 4) * a->n_sm)); };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
     auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
@@ -442,7 +446,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.x = a->x; mv.norm_w = w.norm; mv.eps = d.norm_eps; mv.W = w.wqkv; mv.bias = w.bqkv; mv.N = nqkv; mv.K = dim; mv.y = a->qkv;
             mv.qd = w.qd; mv.kd = w.kd; mv.vd = w.vd; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
             if (routed) { mv.Wr = w.router; mv.E = l.n_experts; mv.z = a->z; }
-            mv.ksplit = pick_ksplit(nqkv + mv.E, dim);
+            mv.ksplit = pick_ksplit(nqkv + mv.E, dim); mv.prefetch = a->opt_prefetch;
             pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(nqkv + mv.E, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
             if (routed) {
                 // gate | up of the chosen experts: reads x and the router logits only, so it runs on the side stream while the main
@@ -486,7 +490,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             PaMv mv{};
             mv.x = a->att; mv.W = w.wo; mv.bias = w.bo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
             if (!routed) mv.residual = a->x; // no feed-forward: the layer ends here
-            mv.ksplit = pick_ksplit(dim, w.od);
+            mv.ksplit = pick_ksplit(dim, w.od); mv.prefetch = a->opt_prefetch;
             pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(dim, mv.ksplit)), dim3(PA_DV_THREADS), 0, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
@@ -560,7 +564,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         if (single) {
             PaMv mv{};
             mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
-            mv.ksplit = pick_ksplit(d.vocab_size, dim);
+            mv.ksplit = pick_ksplit(d.vocab_size, dim); mv.prefetch = a->opt_prefetch;
             pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(d.vocab_size, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);

@@ -5,7 +5,8 @@
 //                          norm of the residual stream in the prologue (q|k|v + router rows, lm_head),
 //                          bias, K row / V^T column straight into the cache, router logits from the UNROUNDED fp32 input,
 //                          residual add (output projection of a layer without a feed-forward)
-//   pa_k_dec_scores      scores of all heads for 32 keys per CTA (warp per key, coalesced K rows), head mixing, distance bias
+//   pa_k_dec_scores      scores of all heads for 16 keys per CTA (thread per key and head out of shared memory), distance bias, head
+//                        mixing, per-block soft-max statistics
 //   pa_k_dec_pv          soft-max statistics (+ sink) per head, weights staged once per CTA, P.V along contiguous V^T rows
 //   pa_k_dec_expert_up   norm + top-k of the router scores in the prologue, gate | up rows of the chosen experts, activation
 //   pa_k_dec_expert_down down rows of the chosen experts summed over the slots + mixer output + residual
@@ -100,6 +101,7 @@ struct PaMv {
     int E;
     float *z;
     int ksplit;            // warps of a CTA that share a row pair, each taking K / ksplit of the columns (1, 2, 4 or 8)
+    int prefetch;          // 1: request the first row group into L2 before the dependency wait; 2: also every next group one ahead
 };
 
 template <bool ROUND>
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
     auto row = [&](int n) { return n < a.N ? a.W + (int64_t)n * a.K : a.Wr + (int64_t)(n - a.N) * a.K; };
     auto prefetch = [&](int grp) {
         const int n0 = (grp * pairs + pair) * 2;
-        if (n0 < total) pa_prefetch2(row(n0), row(min(n0 + 1, total - 1)), k_begin, k_end, lane);
+        if (a.prefetch && n0 < total) pa_prefetch2(row(n0), row(min(n0 + 1, total - 1)), k_begin, k_end, lane);
     };
     prefetch(blockIdx.x);
     // launched with programmatic stream serialisation: everything above touches weights only and overlaps the kernel before
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
         xin = pa_hs;
     }
     for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
-        if (grp + (int)gridDim.x < groups) prefetch(grp + gridDim.x); // the next group's rows travel to L2 while this one is summed
+        if (a.prefetch > 1 && grp + (int)gridDim.x < groups) prefetch(grp + gridDim.x); // opt-in: the next group's rows travel to L2 meanwhile
         const int n0 = (grp * pairs + pair) * 2, n1 = min(n0 + 1, total - 1);
         const bool live = n0 < total;
         float s0 = 0.f, s1 = 0.f;
@@ -174,19 +176,19 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
 }
 
 // ---------------------------------------------------------------------------------------------------- decode attention
-// b[h][j] for the CTA's PA_DS_KEYS keys.  The keys' cache rows are ONE contiguous region: a single 1-D bulk copy brings them to
-// shared memory while the threads fetch q and the mixing matrix; then a warp per key forms the raw scores of every head (a kv
-// group's query heads reuse the key element), applies scale / temperature / distance bias, and the heads are mixed.
+// b[h][j] for the CTA's PA_DS_KEYS keys.  The keys' cache rows arrive in shared memory by 1-D bulk copies (one per row, the rows
+// padded against bank conflicts) while the threads fetch q; then a thread per (key, head) forms the dot product with float4 reads
+// and applies scale / temperature / distance bias - no shuffles, and the bias look-ups of all pairs are in flight together.
 __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *__restrict__ q, const float *__restrict__ kc, const int32_t *__restrict__ pos_dev,
                                                        float *__restrict__ b, int *__restrict__ err) {
     extern __shared__ __align__(16) float sm[];
     __shared__ __align__(8) uint64_t bar;
-    const int H = at.H, G = at.G, dq = at.dq, rep = H / G, kd = G * dq;
-    float *ks = sm;                        // [PA_DS_KEYS][kd]
-    float *qs = ks + PA_DS_KEYS * kd;      // [H][dq]
-    float *sa = qs + H * dq;               // [PA_DS_KEYS][H]
-    float *Ts = sa + PA_DS_KEYS * H;       // [H][H]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = at.H, G = at.G, dq = at.dq, rep = H / G, kd = G * dq, kds = ((kd + 3) & ~3) + 4;
+    float *ks = sm;                        // [PA_DS_KEYS][kds]
+    float *qs = ks + PA_DS_KEYS * kds;     // [H][dq]
+    float *sa = qs + H * dq;               // [H][PA_DS_KEYS + 1]
+    float *Ts = sa + H * (PA_DS_KEYS + 1); // [H][H]
+    const int tid = threadIdx.x;
     if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t]; // a weight: fetched before the dependency wait
     ps_grid_dep_launch();
     ps_grid_dep_wait();
@@ -199,40 +201,30 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
         ps_fence_barrier_init();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         ps_mbar_expect_tx(&bar, (uint32_t)(nj * kd * 4));
-        ps_bulk_g2s(ks, kc + (int64_t)j0 * kd, (uint32_t)(nj * kd * 4), &bar);
+        for (int jj = 0; jj < nj; jj++) ps_bulk_g2s(ks + jj * kds, kc + (int64_t)(j0 + jj) * kd, (uint32_t)(kd * 4), &bar);
     }
-    if (!bulk) for (int t = tid; t < nj * kd; t += 256) ks[t] = kc[(int64_t)j0 * kd + t];
+    if (!bulk) for (int t = tid; t < nj * kd; t += 256) ks[(t / kd) * kds + t % kd] = kc[(int64_t)j0 * kd + t];
     for (int t = tid; t < H * dq; t += 256) qs[t] = q[t];
     __syncthreads();
     if (bulk && !ps_tc_wait(&bar, 0)) { if (tid == 0) err[0] = 5; return; }
-    for (int jj = warp; jj < nj; jj += 8) {
-        const float *krow = ks + jj * kd;
-        for (int g = 0; g < G; g++) {
-            for (int r0 = 0; r0 < rep; r0 += 4) {
-                float s[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int d = lane; d < dq; d += 32) {
-                    const float kv = krow[g * dq + d];
-#pragma unroll
-                    for (int r = 0; r < 4; r++)
-                        if (r0 + r < rep) s[r] = fmaf(kv, qs[(g * rep + r0 + r) * dq + d], s[r]);
-                }
-#pragma unroll
-                for (int r = 0; r < 4; r++) {
-                    if (r0 + r >= rep) break;
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
-                }
-                if (lane == 0) {
-#pragma unroll
-                    for (int r = 0; r < 4; r++)
-                        if (r0 + r < rep) sa[jj * H + g * rep + r0 + r] = s[r];
-                }
+    for (int t = tid; t < PA_DS_KEYS * H; t += 256) {
+        const int jj = t % PA_DS_KEYS, h = t / PA_DS_KEYS;
+        if (jj >= nj) continue;
+        const float *kr = ks + jj * kds + (h / rep) * dq, *qr = qs + h * dq;
+        float s;
+        if ((dq & 3) == 0) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int d = 0; d < dq; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4 *>(kr + d), q4 = *reinterpret_cast<const float4 *>(qr + d);
+                acc.x = fmaf(k4.x, q4.x, acc.x); acc.y = fmaf(k4.y, q4.y, acc.y); acc.z = fmaf(k4.z, q4.z, acc.z); acc.w = fmaf(k4.w, q4.w, acc.w);
             }
+            s = (acc.x + acc.y) + (acc.z + acc.w);
+        } else {
+            s = 0.f;
+            for (int d = 0; d < dq; d++) s = fmaf(kr[d], qr[d], s);
         }
+        sa[h * (PA_DS_KEYS + 1) + jj] = pa_score(at, s, h, pos - (j0 + jj));
     }
-    __syncthreads();
-    // scale / temperature / distance bias for every (key, head) at once: the table look-ups are dependent global loads
-    for (int t = tid; t < nj * H; t += 256) sa[t] = pa_score(at, sa[t], t % H, pos - (j0 + t / H));
     __syncthreads();
     // mix the heads, store, and leave the block's soft-max statistics (max, sum of exponentials) for the P.V kernel:
     // the 16 keys of a head sit in 16 adjacent lanes
@@ -244,9 +236,9 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
         if (valid) {
             if (at.mix) {
                 s = 0.f;
-                for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[jj * H + g], s);
+                for (int g = 0; g < H; g++) s = fmaf(Ts[h * H + g], sa[g * (PA_DS_KEYS + 1) + jj], s);
             } else {
-                s = sa[jj * H + h];
+                s = sa[h * (PA_DS_KEYS + 1) + jj];
             }
             b[(int64_t)h * at.ldS + j0 + jj] = s;
         }
@@ -398,8 +390,6 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
     const int rows = PA_DV_ROWS / 2;
     for (int n = blockIdx.x * rows + warp; n < ff; n += gridDim.x * rows) {
         const bf16 *wg = Wg + ((int64_t)e * ff + n) * dim, *wu = Wu + ((int64_t)e * ff + n) * dim;
-        const int nn = n + gridDim.x * rows;
-        if (nn < ff) pa_prefetch2(wg + (int64_t)gridDim.x * rows * dim, wu + (int64_t)gridDim.x * rows * dim, 0, dim, lane);
         float gsum, usum;
         pa_dot2<ROUND>(wg, wu, pa_hs, dim, w, lane, gsum, usum);
         if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);

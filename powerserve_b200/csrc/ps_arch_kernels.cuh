@@ -78,7 +78,20 @@ __device__ __forceinline__ void pa_tile_mm(float (&acc)[NB][4][4], const float *
 __global__ void __launch_bounds__(128) pa_k_embed(float *__restrict__ x, const bf16 *__restrict__ table, const int32_t *__restrict__ tokens, int dim, float scale) {
     const int t = blockIdx.x;
     const bf16 *row = table + (int64_t)tokens[t] * dim;
-    for (int c = threadIdx.x; c < dim; c += blockDim.x) x[(int64_t)t * dim + c] = __bfloat162float(row[c]) * scale;
+    float *out = x + (int64_t)t * dim;
+    if ((dim & 7) == 0) { // 16-byte loads: the whole row is in flight at once
+        for (int c = threadIdx.x * 8; c < dim; c += blockDim.x * 8) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row + c));
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                out[c + 2 * i] = __uint_as_float(u[i] << 16) * scale;
+                out[c + 2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u) * scale;
+            }
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) out[c] = __bfloat162float(row[c]) * scale;
 }
 
 // h = x / sqrt(mean(x^2) + eps) * w   (w already holds 1 + weight for unit-offset norms)

@@ -2771,9 +2771,9 @@ int ps_cuda_tp_init(ps_cuda_ctx *ctx, const void *id128) {
 }
 
 int ps_cuda_set_option(ps_cuda_ctx *ctx, const char *name, int value) {
-    if (ctx->arch && ps_arch_set_option(ctx->arch, name, value)) return 0;
-    if (ctx->g_step) { cudaGraphExecDestroy(ctx->g_step); ctx->g_step = nullptr; }
+    if (ctx->g_step) { cudaGraphExecDestroy(ctx->g_step); ctx->g_step = nullptr; } // a captured step holds the old choice
     if (ctx->g_fwd) { cudaGraphExecDestroy(ctx->g_fwd); ctx->g_fwd = nullptr; }
+    if (ctx->arch && ps_arch_set_option(ctx->arch, name, value)) return 0;
     if (!strcmp(name, "graph")) ctx->opt_graph = value;
     else if (!strcmp(name, "fused")) {
         if (!value && ctx->tp > 1) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "option fused = 0: the table-op path is not sharded; tensor-parallel contexts run the fused path only");
