@@ -61,7 +61,7 @@ struct PsArch {
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int opt_fork = 1;
-    int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, else four)
+    int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, four for long streams or without overlap)
     int opt_prefetch = 1; // 1: a mat-vec CTA requests its first row group into L2 before the dependency wait; 2: every next group too
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
 };
@@ -415,7 +415,11 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     // the mat-vec CTAs walk the row groups with the grid's stride: at most four resident CTAs per SM, one wave
     // (two per SM when the launches overlap: the next kernel's CTAs need room beside them to fetch their weights early)
     const bool pdl = a->opt_pdl != 0;
-    auto mv_grid = [&](int rows, int ks) { return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)((a->opt_mv_cap > 0 ? a->opt_mv_cap : pdl ? 2 : 4) * a->n_sm)); };
+    auto mv_grid = [&](int rows, int ks, int K) {
+        // a long stream (>= 48 MB) gains more from four resident CTAs per SM than from the next kernel's early start
+        const int cap = a->opt_mv_cap > 0 ? a->opt_mv_cap : (!pdl || (int64_t)rows * K * 2 >= ((int64_t)48 << 20)) ? 4 : 2;
+        return std::min(cdiv(rows, PA_DV_ROWS / ks), (unsigned)(cap * a->n_sm));
+    };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
     auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
@@ -447,7 +451,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.qd = w.qd; mv.kd = w.kd; mv.vd = w.vd; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
             if (routed) { mv.Wr = w.router; mv.E = l.n_experts; mv.z = a->z; }
             mv.ksplit = pick_ksplit(nqkv + mv.E, dim); mv.prefetch = a->opt_prefetch;
-            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(nqkv + mv.E, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(nqkv + mv.E, mv.ksplit, dim)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
             if (routed) {
                 // gate | up of the chosen experts: reads x and the router logits only, so it runs on the side stream while the main
                 // stream goes through scores, P.V and the output projection (a fork in the captured graph); joined before `down`
@@ -491,7 +495,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             mv.x = a->att; mv.W = w.wo; mv.bias = w.bo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
             if (!routed) mv.residual = a->x; // no feed-forward: the layer ends here
             mv.ksplit = pick_ksplit(dim, w.od); mv.prefetch = a->opt_prefetch;
-            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(dim, mv.ksplit)), dim3(PA_DV_THREADS), 0, st, mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(dim, mv.ksplit, w.od)), dim3(PA_DV_THREADS), 0, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->att, w.od, bs, w.od, w.t_o, dim, w.bo, a->ao, dim);
             if (rc) return rc;
@@ -565,7 +569,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             PaMv mv{};
             mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
             mv.ksplit = pick_ksplit(d.vocab_size, dim); mv.prefetch = a->opt_prefetch;
-            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(d.vocab_size, mv.ksplit)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
+            pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(d.vocab_size, mv.ksplit, dim)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
         } else if (tc) {
             int rc = tc_dense(a->h, dim, bs, dim, a->t_head, d.vocab_size, nullptr, a->logits, d.vocab_size);
             if (rc) return rc;
