@@ -453,7 +453,7 @@ float ps_or_vec_dot(int wtype, int64_t k, const void *w, const void *xq) {
 
 /* ggml_vec_dot_f32, AVX branch: GGML_F32_STEP 32, 4 accumulators x 8 lanes, GGML_F32x8_REDUCE (ggml.c:1354-1372),
  * scalar leftovers (ggml.c:2092-2131).  The leftover `sumf += x[i]*y[i]` is NOT fused in the reference build: gcc
- * vectorises the products (vmulps) and adds them to sumf one by one, in order (vaddss) — objdump of oracle/_ref. */
+ * vectorises the products (vmulps) and adds them to sumf one by one, in order (vaddss) (as the compiled reference does). */
 float ps_or_vec_dot_f32(int64_t n, const float *x, const float *y) {
     const int64_t np = n & ~(int64_t)31;
     float sum[4][8];
@@ -512,7 +512,7 @@ void ps_or_rmsnorm(float *dst, const float *x, const float *w, int64_t dim, int6
 /* ggml_compute_forward_rope_f32, ggml.c:15368-15497 with ggml_rope_cache_init :15342-15356 and rope_yarn
  * :15319-15336 at ext_factor = 0, freq_factors = NULL.  src/dst: {head_size, n_heads, bs}.
  * The rotation `x0*c - x1*s`, `x0*s + x1*c` is NOT fused in the reference build: gcc emits four vmulss/vmulps and
- * a vsubss/vaddss (vaddsubps when vectorised) — objdump of oracle/_ref; so every product is rounded to fp32. */
+ * a vsubss/vaddss (vaddsubps when vectorised); so every product is rounded to fp32. */
 void ps_or_rope(float *dst, const float *src, int64_t head_size, int64_t n_heads, int64_t bs, const int32_t *pos,
                 int n_dims, int mode, float freq_base, float freq_scale, float attn_factor) {
     const float theta_scale = powf(freq_base, -2.0f / n_dims);

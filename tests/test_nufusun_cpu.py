@@ -41,7 +41,7 @@ def test_bf16_rounding_is_nearest_even():
     np.testing.assert_array_equal((bits.astype(np.uint32) << 16).view(np.float32), got)
 
 
-@pytest.mark.parametrize("rows,dmax", [(32, 120.0), (16, 100.0), (8, 64.0), (10, 33.0), (9, 50.0), (4, 3.5), (64, 1000.0)])
+@pytest.mark.parametrize("rows,dmax", [(32, 200.0), (16, 100.0), (8, 64.0), (10, 33.0), (9, 50.0), (4, 3.5), (64, 1000.0)])
 def test_host_bucket_table_matches_formula(lib, rows, dmax):
     half = rows // 2
     prev = -1
