@@ -44,8 +44,8 @@ def peaks():
 
 
 def weight_bytes_per_token(shape: synth.ModelShape) -> int:
-    """Algorithmic bytes of one decoded token: every matmul weight block as stored in the GGUF, read once
-    (SURVEY.md section 8(d)): 7 matrices per layer + lm_head."""
+    """Algorithmic bytes of one decoded token: every matmul weight block as stored in the GGUF, read once:
+    7 matrices per layer + lm_head."""
     n = 0
     for name, t, shp, _ in synth.tensor_plan(shape):
         if t != gguf.GGML_F32 and name != "token_embd.weight":
@@ -224,7 +224,7 @@ def extra_config0_qwen2(args, hbm_peak):
 
 
 def extra_sessions(model, shape, hbm_peak, n_sess=64, n_steps=24):
-    """Server-side batching (SURVEY section 8 f4) on the benchmarked model: n_sess independent sessions (own KV sets, 32-token
+    """Server-side batching on the benchmarked model: n_sess independent sessions (own KV sets, 32-token
     prompts) advanced one token each per forward pass through ps_cuda_forward_sessions - one weight stream per pass, so the
     aggregate rate may exceed the one-sequence HBM roofline.  Device time of the passes; ids come back, logits stay on the device."""
     sids = [0] + [model.session_create() for _ in range(n_sess - 1)]
@@ -543,7 +543,7 @@ def main():
                     closed = True
                     out["e2e_powerserve_stack"] = extra_powerserve_stack(md.path, shape, args.prompt, min(args.steps, 64), cpu_threads)
                     lazy = extra_powerserve_stack(md.path, shape, args.prompt, min(args.steps, 64), cpu_threads, device_topk=40)
-                    lazy["what"] = "the same stack with device-side sampling (SURVEY 8 f3): logits stay on the device, TopKSampler(40) runs there, 80 words per token cross PCIe"
+                    lazy["what"] = "the same stack with device-side sampling: logits stay on the device, TopKSampler(40) runs there, 80 words per token cross PCIe"
                     out["e2e_powerserve_stack_device_topk"] = lazy
                 if world == 1:
                     cp = synth.random_prompt(shape.vocab_size, 17, seed=1234)

@@ -11,7 +11,7 @@
  *   - every call enqueues on the context's stream and returns an int status: 0 = ok, otherwise an error whose text
  *     `ps_cuda_last_error` returns.  The C++ side converts non-zero into POWERSERVE_ABORT to keep the reference's
  *     error convention (src/core/logger.hpp:56-82).
- *   - results are BIT-IDENTICAL to the reference's x86 AVX2+FMA build (see DESIGN.md "Numerics contract").
+ *   - results are BIT-IDENTICAL to the reference's x86 AVX2+FMA build.
  *   - there is NO CPU fallback: without a CUDA device every entry point fails (PS_CUDA_ERR_NO_DEVICE).
  */
 #ifndef PS_CUDA_H
@@ -96,7 +96,7 @@ int ps_cuda_rmsnorm(ps_cuda_ctx *ctx, float *dst, const float *x, const float *w
 int ps_cuda_matmul(ps_cuda_ctx *ctx, float *dst, const void *w, int wtype, int64_t K, int64_t N, const float *x, int64_t bs);
 int ps_cuda_rope(ps_cuda_ctx *ctx, float *dst, const float *src, int64_t head_size, int64_t n_heads, int64_t bs, const int32_t *pos);
 /* RoPE frequency factors (rope_freqs.weight of Llama-3.1 / 3.2 GGUFs; ggml_rope_cache_init, ggml.c:15342-15356: theta / ff).
- * The reference never passes them (ggml_wrapper.cpp:104-106, SURVEY F6), so the default - and parity - is WITHOUT;
+ * The reference never passes them (ggml_wrapper.cpp:104-106), so the default - and parity - is WITHOUT;
  * factors == NULL restores that.  n must be rope_n_dims / 2.  Rebuilds the context's cos / sin table. */
 int ps_cuda_set_rope_freq_factors(ps_cuda_ctx *ctx, const float *factors, int n);
 int ps_cuda_add(ps_cuda_ctx *ctx, float *dst, const float *a, const float *b, int64_t n, int64_t nb); /* b row-broadcast */
@@ -161,7 +161,7 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
 int ps_cuda_forward_tree(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos, int bs, const uint8_t *tree_mask, int lm_head,
                          float *logits_host);
 /* ---------------------------------------------------------------------------------------------- sessions
- * Server-side batching (SURVEY.md section 8 f4; app/server/server_handler.hpp:512-720): the reference serves one generation
+ * Server-side batching (app/server/server_handler.hpp:512-720): the reference serves one generation
  * per model at a time because the KV position is shared state (server_handler.hpp:224-240).  A context can hold several
  * independent KV sets over one set of weights.  Session 0 is the context's own cache.  ps_cuda_session_select makes a
  * session the target of every single-sequence call (forward / forward_tree / decode_greedy / kv_*), so prefill and KV
@@ -182,7 +182,7 @@ int ps_cuda_forward_sessions(ps_cuda_ctx *ctx, const int32_t *session_ids, const
 int ps_cuda_decode_greedy(ps_cuda_ctx *ctx, int32_t first_token, int n_steps, int32_t *ids_host);
 /* device-side logits of the last forward ([bs][vocab]) for callers that sample on the GPU */
 const float *ps_cuda_logits_dev(ps_cuda_ctx *ctx);
-/* Device-side sampling (SURVEY.md section 8 f3): ps_cuda_forward / ps_cuda_forward_sessions accept logits_host == NULL with
+/* Device-side sampling: ps_cuda_forward / ps_cuda_forward_sessions accept logits_host == NULL with
  * lm_head = 1 - the logits stay on the device - and ps_cuda_sample_topk returns what ProbArray holds after
  * TopKSampler::apply (src/sampler/sampler.cpp:39-56, prob_array.hpp:43-49): the k <= 64 largest logits of row `row` of the
  * last forward pass, descending (equal logits by ascending token id), with their token ids.  2 k words cross PCIe instead of

@@ -477,7 +477,7 @@ float ps_or_vec_dot_f32(int64_t n, const float *x, const float *y) {
 /* ------------------------------------------------------------------------------------------------ operators */
 /* powerserve_compute_forward_mul_mat, ggml.c:13434-13648: quantise every src1 row to vec_dot_type (:13502-13530),
  * then dst[n, b] = vec_dot(W row n, xq row b) (:13344-13432).  Each output is produced by one vec_dot call, so the
- * result is independent of the thread count (SURVEY F4). */
+ * result is independent of the thread count. */
 typedef struct { int wtype; const void *w; int64_t K, N, bs; float *dst; const char *xq; size_t xrow, wrow; } mm_ctx;
 static void mm_rows(int64_t n0, int64_t n1, void *p) {
     const mm_ctx *c = (const mm_ctx *)p;
@@ -510,7 +510,7 @@ void ps_or_rmsnorm(float *dst, const float *x, const float *w, int64_t dim, int6
 }
 
 /* ggml_compute_forward_rope_f32, ggml.c:15368-15497 with ggml_rope_cache_init :15342-15356 and rope_yarn
- * :15319-15336 at ext_factor = 0, freq_factors = NULL (SURVEY F6).  src/dst: {head_size, n_heads, bs}.
+ * :15319-15336 at ext_factor = 0, freq_factors = NULL.  src/dst: {head_size, n_heads, bs}.
  * The rotation `x0*c - x1*s`, `x0*s + x1*c` is NOT fused in the reference build: gcc emits four vmulss/vmulps and
  * a vsubss/vaddss (vaddsubps when vectorised); so every product is rounded to fp32. */
 void ps_or_rope(float *dst, const float *src, int64_t head_size, int64_t n_heads, int64_t bs, const int32_t *pos,
@@ -550,7 +550,7 @@ void ps_or_rope(float *dst, const float *src, int64_t head_size, int64_t n_heads
     free(cache);
 }
 
-/* GET_MASK, src/executor/executor.cpp:210-224: positions only, the tree mask is ignored (SURVEY F7) */
+/* GET_MASK, src/executor/executor.cpp:210-224: positions only, the tree mask is ignored */
 void ps_or_get_mask(float *mask, int64_t n_kv, int64_t bs, const int32_t *pos) {
     for (int64_t i = 0; i < bs; i++)
         for (int64_t j = 0; j < n_kv; j++) mask[j + i * n_kv] = (j <= (int64_t)pos[i]) ? 0.f : -INFINITY;

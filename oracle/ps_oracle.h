@@ -3,7 +3,7 @@
  * CPU restatement (plain C) of the arithmetic PowerServe's ggml CPU backend performs on the decode/prefill hot
  * path, as compiled for x86-64 AVX2+FMA+F16C (the reference's Release build with GGML_NATIVE=OFF).  The goal is
  * BIT-EXACT agreement with that build: the reference quantises activations before every weight matmul
- *  and a 1-ulp difference anywhere upstream of a quantiser is amplified to percent-level logit
+ * and a 1-ulp difference anywhere upstream of a quantiser is amplified to percent-level logit
  * noise within one forward pass (F13), so "close" is not a usable parity criterion — identical is.
  *
  * Pinned by tests/test_oracle_vs_ref.py against oracle/_ref/libggml_ref.so (the reference's own ggml compiled from

@@ -3,7 +3,7 @@
     python -m powerserve_b200.build [--force]
 
 nvcc cross-compiles for sm_100a without a GPU; the resulting .so sits next to this file (git-ignored, but it
-travels to the GPU box with gpurun).
+travels to the GPU box with the tree).
 """
 from __future__ import annotations
 

@@ -280,7 +280,7 @@ class CudaBackend:
         self._ck(self.L.ps_cuda_copy_2d(self.h, dst.ptr, ds0, ds1, src.ptr, ss0, ss1, ne0, ne1))
 
     def set_rope_freq_factors(self, factors):
-        """rope_freqs.weight (off by default: the reference ignores it, SURVEY F6); None restores the default"""
+        """rope_freqs.weight (off by default: the reference ignores it); None restores the default"""
         if factors is None:
             self._ck(self.L.ps_cuda_set_rope_freq_factors(self.h, None, 0))
         else:

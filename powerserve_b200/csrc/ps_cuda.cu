@@ -80,7 +80,7 @@ struct ps_cuda_ctx {
     cudaStream_t stream = nullptr;
     ps_cuda_model_desc d{};
     std::string err;
-    std::mutex mu; // one in-flight generation per context (SURVEY 8b "Threading")
+    std::mutex mu; // one in-flight generation per context
     std::unordered_map<const void *, DevWeight> weights;
     std::vector<void *> owned; // every cudaMalloc we must free
     std::unordered_set<void *> pooled; // ps_cuda_malloc blocks: stream-ordered pool (CUDABuffer intermediates come and go every forward pass)
@@ -93,7 +93,7 @@ struct ps_cuda_ctx {
     // kv cache
     std::vector<float *> kc, vct;
     int position = 0;
-    // server-side batching (SURVEY 8 f4): independent KV sets over one set of weights; the ACTIVE session's state lives in kc / vct /
+    // server-side batching: independent KV sets over one set of weights; the ACTIVE session's state lives in kc / vct /
     // position / slot_mask above, the others are parked here
     struct KvSet { std::vector<float *> kc, vct; int position = 0; std::vector<uint8_t> slot_mask; };
     std::unordered_map<int, KvSet> sessions;
@@ -140,7 +140,7 @@ struct ps_cuda_ctx {
     uint8_t *rw_out = nullptr; // lm_head, octet-interleaved
     uint8_t *tc_out = nullptr; // lm_head, fp16-expanded tensor-core operand (batches of 16+ columns that want logits: session batches, verify batches)
     bool fused_ok = false;   // every matmul weight (and the embedding) is Q4_K: the fused decode path applies
-    int opt_attn_group = 0;  // opt-in: decode attention as ONE group-synchronised kernel per layer (ps_k_attn_group); bit-exact, but 23 us vs 11.7 us per layer at ctx 2048 (DESIGN.md 5b)
+    int opt_attn_group = 0;  // opt-in: decode attention as ONE group-synchronised kernel per layer (ps_k_attn_group); bit-exact, but 23 us vs 11.7 us per layer at ctx 2048
     unsigned long long *ag_ctr = nullptr; // [n_layers][n_kv_heads] arrival counters of the kv-head groups
     float *ag_max = nullptr;              // [n_kv_heads][hs / 8][8] chunk maxima
     double *ag_sum = nullptr;             // [n_kv_heads][hs / 8][8] chunk sums
@@ -151,7 +151,7 @@ struct ps_cuda_ctx {
     int opt_ops_graph = 1;
     int n_sm = 148;
     int32_t *ctr_dev = nullptr;
-    // tensor parallelism (row sharding of every matrix + all-gather, bit-exact; DESIGN.md): local sizes of this rank
+    // tensor parallelism (row sharding of every matrix + all-gather, bit-exact): local sizes of this rank
     int tp = 1, rank = 0;
     int nh_l = 0, nkv_l = 0, ffn_l = 0, vocab_l = 0, dim_l = 0;
     void *nccl_comm = nullptr;
@@ -184,7 +184,7 @@ struct ps_cuda_ctx {
     int64_t g_step_kernels = 0, g_fwd_kernels = 0;     // kernels captured in each
     int attn_clusters = -1;                            // cudaOccupancyMaxActiveClusters of the fused attention kernel (counter "attn_clusters")
     // persistent per-step kernel (ps_step.cuh)
-    int opt_persist = 0;            // 1: the whole decode step as ONE persistent kernel (ps_step.cuh); bit-exact and tested, but 2x slower than the per-phase kernels so far (DESIGN.md)
+    int opt_persist = 0;            // 1: the whole decode step as ONE persistent kernel (ps_step.cuh); bit-exact and tested, but 2x slower than the per-phase kernels so far
     int opt_l2_ahead = 96;          // stages (4736 B) per CTA the L2 look-ahead warp stays ahead of the shared-memory rings (0 = off)
     int opt_attn_chunk = 0;         // testing: cap on the soft-max positions resident in shared memory (forces the chunked attention path)
     bool step_ok = false;           // the model / geometry qualifies for ps_k_step
@@ -268,10 +268,10 @@ bool type_ok(int t) { return t == 0 || t == 1 || t == 2 || t == 8 || t == 12 || 
 int blk_elems(int t) { return (t == 12 || t == 13 || t == 14) ? 256 : (t <= 1 ? 1 : 32); }
 
 // ggml_rope_cache_init (libs/ggml/src/ggml.c:15342-15356) + rope_yarn (:15319-15336) at ext_factor == 0,
-// freq_factors == NULL (src/backend/ggml/ggml_wrapper.cpp:104-106, SURVEY F6), evaluated with the platform libm for
+// freq_factors == NULL (src/backend/ggml/ggml_wrapper.cpp:104-106), evaluated with the platform libm for
 // every position once.
 // `ff` (optional, n_dims / 2 entries): the freq_factors of ggml_rope_cache_init - theta / ff[i0 / 2] enters rope_yarn (the
-// "llama3" rope scaling of Llama-3.1 / 3.2 GGUFs, rope_freqs.weight).  The reference never passes them (SURVEY F6), so they
+// "llama3" rope scaling of Llama-3.1 / 3.2 GGUFs, rope_freqs.weight).  The reference never passes them, so they
 // are off unless ps_cuda_set_rope_freq_factors is called.
 void build_rope_table(const ps_cuda_model_desc &d, std::vector<float> &t, const float *ff = nullptr) {
     const int hs = d.head_size;
@@ -2254,7 +2254,7 @@ static int check_forward_args(ps_cuda_ctx *ctx, const int32_t *tokens, const int
     if (bs <= 0 || bs > ctx->d.max_batch) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: batch %d outside [1,%d]", bs, ctx->d.max_batch);
     for (int i = 0; i < bs; i++) {
         if (tokens[i] < 0 || tokens[i] >= ctx->d.vocab_size) return fail(ctx, PS_CUDA_ERR_INVALID, "forward: token %d outside the vocabulary", tokens[i]);
-        if (pos[i] != pos[0] + i) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "forward: positions must be consecutive (the CPU path ignores tree masks, SURVEY F7)");
+        if (pos[i] != pos[0] + i) return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "forward: positions must be consecutive (the CPU path ignores tree masks)");
     }
     if (pos[0] < 0 || pos[0] + bs > ctx->d.n_ctx) return fail(ctx, PS_CUDA_ERR_KV_FULL, "the length of kvcache is up to the preset threshold: %d", ctx->d.n_ctx);
     return 0;
@@ -2284,7 +2284,7 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
     } else if (ctx->tp > 1 && bs > 1) {
         // tensor parallel without NCCL (or option tp_batch = 0): the sharded single-token step is fed token by token, i.e.
         // it equals the reference run with batch_size = 1 (NOT a batched pass: the reference's soft-max row length and its
-        // SIMD / libm exp split depend on the chunking, DESIGN.md section 6)
+        // SIMD / libm exp split depend on the chunking)
         for (int i = 0; i < bs && !rc; i++) {
             PS_CK(cudaMemcpyAsync(ctx->tokens_dev, ctx->h_tokens + i, 4, cudaMemcpyHostToDevice, ctx->stream));
             PS_CK(cudaMemcpyAsync(ctx->pos_dev, ctx->h_pos + i, 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -2329,7 +2329,7 @@ int ps_cuda_forward(ps_cuda_ctx *ctx, const int32_t *tokens, const int32_t *pos,
 }
 
 // ---------------------------------------------------------------------------------------------- sessions (server-side batching)
-// SURVEY section 8 f4 (app/server/server_handler.hpp:512-720): the reference serves one generation per model at a time - its
+// Server-side batching (app/server/server_handler.hpp:512-720): the reference serves one generation per model at a time - its
 // KV position is shared state.  Here a context can hold several independent KV sets ("sessions") over ONE set of weights:
 // ps_cuda_session_select makes one of them the target of every single-sequence call (forward / decode_greedy / kv_*: prefill
 // and bookkeeping work unchanged), and ps_cuda_forward_sessions advances n sessions by one token each in ONE forward pass -
@@ -2790,8 +2790,8 @@ int ps_cuda_set_option(ps_cuda_ctx *ctx, const char *name, int value) {
     else if (!strcmp(name, "attn_tile")) ctx->opt_attn_tile = value; // register-tiled scores / P.V kernels for batches (0: the first-generation kernels, for A/B)
     else if (!strcmp(name, "pv_batch_min")) ctx->opt_pv_batch_min = value; // batches at least this wide use the query-blocked P.V kernel (prefill), narrower ones the per-(head, dim) warp kernel
     else if (!strcmp(name, "rw_unroll2")) ctx->opt_unroll2 = value; // tuning: two blocks per loop trip in the mat-vec launches with <= 8 octets per CTA
-    else if (!strcmp(name, "attn_group")) ctx->opt_attn_group = value; // 1: decode attention as one group-synchronised kernel per layer (bit-exact, slower so far: DESIGN.md 5b); 0 (default): scores kernel + soft-max / P.V kernel
-    else if (!strcmp(name, "attn_fused")) ctx->opt_attn_fused = value; // 1: decode attention as ONE cluster kernel per layer (bit-exact, but slower so far: DESIGN.md); 0 (default): scores kernel + soft-max / P.V kernel
+    else if (!strcmp(name, "attn_group")) ctx->opt_attn_group = value; // 1: decode attention as one group-synchronised kernel per layer (bit-exact, slower so far); 0 (default): scores kernel + soft-max / P.V kernel
+    else if (!strcmp(name, "attn_fused")) ctx->opt_attn_fused = value; // 1: decode attention as ONE cluster kernel per layer (bit-exact, but slower so far); 0 (default): scores kernel + soft-max / P.V kernel
     else if (!strcmp(name, "l2_ahead")) ctx->opt_l2_ahead = value;     // tuning: L2 look-ahead of the step kernel's weight stream, in 4736-byte stages per CTA
     else if (!strcmp(name, "attn_chunk")) ctx->opt_attn_chunk = value; // testing: soft-max positions resident in shared memory (multiple of 256)
     else if (!strcmp(name, "persist")) ctx->opt_persist = value; // 1: the whole decode step as ONE persistent kernel (ps_step.cuh); 0 (default): one kernel per phase

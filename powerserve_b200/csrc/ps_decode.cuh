@@ -33,7 +33,7 @@ PS_D int ps_dp4a_us(uint32_t a, int b, int c) { // unsigned bytes of a  x  signe
 // publishes a monotonically increasing epoch into flags[slot][my_rank] on every rank (release, system scope).  The
 // consumer kernel of the same phase waits (acquire, system scope) until all ranks' flags have reached the epoch its own
 // rank published in that phase.  Gathers are in place: the barrier chain of the decode step makes every buffer's next
-// write happen after all of its readers are done ("tensor parallelism").
+// write happen after all of its readers are done.
 #define PS_TP_MAX 8
 struct PsTpOut {
     unsigned long long *peer_ll[PS_TP_MAX]; // in-band-flag exchange (else null): (value, epoch) words on every rank, already offset
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(PS_A2_THREADS) ps_k_attn2(float *__restrict__ 
 // head size 128).  All CTAs of a group are co-resident by construction (grid <= SM count, one CTA per SM; the dependent
 // grid starts only after every CTA of this one has started), the waits are bounded all the same (error flag, no hang).
 // Arithmetic = ps_k_attn1 + ps_k_attn2: ggml_vec_dot_f32 lane chains, GGML_F32x8_REDUCE, scale, + 0.0f mask, soft-max with
-// double sums (tree order, DESIGN.md section 2), position-ordered FMA chains for P.V.  norm_attention.cpp:115-151.
+// double sums (tree order), position-ordered FMA chains for P.V.  norm_attention.cpp:115-151.
 // ====================================================================================================================
 #define PS_AG_THREADS 512
 PS_D unsigned long long ps_ag_ld_acquire(const unsigned long long *p) {

@@ -500,7 +500,7 @@ __global__ void __launch_bounds__(256) ps_k_get_embedding(float *__restrict__ ds
     }
 }
 
-// block-wide sum of doubles (tree order; see DESIGN.md "double-precision sums")
+// block-wide sum of doubles (tree order)
 PS_D double ps_block_sum_double(double v, double *sh) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(PS_FULL, v, o);
@@ -570,7 +570,7 @@ __global__ void ps_k_kv_store(float *__restrict__ kc, float *__restrict__ vct, c
     }
 }
 
-// ---- speculative decode (SURVEY section 8 f1): the KV cache as KVCacheInterface sees it (src/core/kv_cache.hpp:97-276) - cache
+// ---- speculative decode: the KV cache as KVCacheInterface sees it (src/core/kv_cache.hpp:97-276) - cache
 // SLOTS decoupled from token positions, a per-slot mask, and the last batch's K / V kept aside for `copy`.
 // KV store of a batch at cache slots base .. base + bs - 1 (save_tokens) + a copy into the per-layer staging rows
 __global__ void ps_k_kv_store_at(float *__restrict__ kc, float *__restrict__ vct, float *__restrict__ k_stage, float *__restrict__ v_stage,
@@ -1118,7 +1118,7 @@ __global__ void __launch_bounds__(128) ps_k_matmul_f32(float *__restrict__ dst, 
 }
 
 // ====================================================================================================================
-// Server-side batching (SURVEY section 8 f4): one token of each of n independent SESSIONS per forward pass.  The weight
+// Server-side batching: one token of each of n independent SESSIONS per forward pass.  The weight
 // products run once for the n columns (one weight stream); attention is per column over that session's OWN cache at its OWN
 // position.  Column `c` = blockIdx.z; kc_ptrs / vct_ptrs hold the session's cache of the current layer, pos[c] its
 // position.  The arithmetic of every column is that of the bs = 1 operator-table kernels above (ps_k_kv_store,
@@ -1222,7 +1222,7 @@ __global__ void __launch_bounds__(128) ps_k_sess_pv(float *__restrict__ out, con
 }
 
 // ====================================================================================================================
-// Device-side top-k (SURVEY section 8 f3): TopKSampler (src/sampler/sampler.cpp:39-56: partial_sort by logit, descending) on the
+// Device-side top-k: TopKSampler (src/sampler/sampler.cpp:39-56: partial_sort by logit, descending) on the
 // device, so that k (logit, token) pairs cross PCIe instead of the vocabulary's logits and the host never builds a
 // vocabulary-sized ProbArray (prob_array.hpp:43-49).  Two stages of repeated arg-max: every CTA extracts the k largest of
 // its slice (kept in shared memory), then one CTA merges the candidates.  Order: logit descending, equal logits by

@@ -1,7 +1,7 @@
 // ps_math.cuh — exact-arithmetic building blocks shared by every kernel.
 //
 // Numerics contract: the CUDA backend reproduces the reference's x86 AVX2+FMA results BIT FOR BIT.  The reference
-// quantises activations before every weight matmul (SURVEY.md F5), so a 1-ulp upstream difference is amplified to
+// quantises activations before every weight matmul, so a 1-ulp upstream difference is amplified to
 // percent-level logit noise in one forward pass (F13); bit-identity is the only stable parity regime.  Rules used
 // throughout:
 //   * every fp32 operation is spelled with an explicit round-to-nearest intrinsic (__fmul_rn / __fadd_rn / __fmaf_rn /

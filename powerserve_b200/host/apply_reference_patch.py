@@ -167,7 +167,7 @@ def patch_model_forward(s):
 """)
 
 
-# ---- Q4_K / Q6_K enablement (SURVEY F1): the reference's DataType layer rejects the K-quants its vendored ggml supports;
+# ---- Q4_K / Q6_K enablement: the reference's DataType layer rejects the K-quants its vendored ggml supports;
 # three enum / switch sites, no arithmetic (the same edit the oracle build applies with sed).
 def patch_data_type(s):
     s = sub(s, "    GGML_Q8_0,\n", "    GGML_Q8_0,\n    GGML_Q4_K,\n    GGML_Q6_K,\n")

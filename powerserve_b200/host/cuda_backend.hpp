@@ -68,7 +68,7 @@ public:
     void forward(const Tensor *out, const std::vector<int> &tokens, const std::vector<int> &pos, bool lm_head);
     // Model::decode with a greedy sampler and no host round trip per token
     std::vector<int> decode_greedy(int first_token, int n_steps);
-    // Device-side sampling (SURVEY 8 f3): with lazy logits `forward` leaves the logits on the device (the CPUBuffer of the
+    // Device-side sampling: with lazy logits `forward` leaves the logits on the device (the CPUBuffer of the
     // CUDA_FORWARD op stays untouched) and topk(k) returns what ProbArray holds after TopKSampler::apply (sampler.cpp:39-56):
     // the k largest (logit, token) pairs, descending - the sampler chain then runs on k entries instead of the vocabulary.
     void set_lazy_logits(bool v) { m_lazy_logits = v; }

@@ -51,7 +51,7 @@ class ModelShape:
 
 
 PRESETS: Dict[str, ModelShape] = {
-    # BASELINE.json configs (SURVEY.md section 8 table)
+    # BASELINE.json configs
     "qwen2-0.5b": ModelShape("qwen2-0.5b", "qwen2", 896, 4864, 24, 14, 2, 64, 151936, True, 2, 1e6, 1e-6, GGML_Q4_0, qkv_bias=True),
     "llama-3.2-1b": ModelShape("llama-3.2-1b", "llama", 2048, 8192, 16, 32, 8, 64, 128256, True, 0, 5e5, 1e-5, GGML_Q4_K),
     "llama-3.1-8b": ModelShape("llama-3.1-8b", "llama", 4096, 14336, 32, 32, 8, 128, 128256, False, 0, 5e5, 1e-5, GGML_Q4_K),
@@ -67,7 +67,7 @@ PRESETS: Dict[str, ModelShape] = {
     # with the next power-of-two template and r2 active heads
     "tiny-qwen2-r7": ModelShape("tiny-qwen2-r7", "qwen2", 448, 608, 2, 7, 1, 64, 512, True, 2, 1e6, 1e-6, GGML_Q4_0, n_ctx=256, qkv_bias=True),
     "tiny-q8-r3": ModelShape("tiny-q8-r3", "llama", 384, 512, 2, 6, 2, 64, 512, False, 0, 1e4, 1e-5, GGML_Q8_0, n_ctx=256),
-    "tiny-q5k": ModelShape("tiny-q5k", "llama", 512, 1024, 2, 8, 2, 64, 768, True, 0, 5e5, 1e-5, GGML_Q5_K, n_ctx=256),   # real-file coverage (SURVEY 8 f2)
+    "tiny-q5k": ModelShape("tiny-q5k", "llama", 512, 1024, 2, 8, 2, 64, 768, True, 0, 5e5, 1e-5, GGML_Q5_K, n_ctx=256),   # real-file coverage
     "tiny-q8": ModelShape("tiny-q8", "llama", 256, 512, 2, 4, 4, 64, 512, False, 0, 1e4, 1e-5, GGML_Q8_0, n_ctx=256),
     # real per-layer shapes of the BASELINE models with few layers / small vocab (exercise nb = 8/32 and 16/56 paths)
     "slice-1b": ModelShape("slice-1b", "llama", 2048, 8192, 2, 32, 8, 64, 2048, True, 0, 5e5, 1e-5, GGML_Q4_K, n_ctx=1024),
@@ -228,5 +228,5 @@ def write_model_dir(path: str, shape: ModelShape, seed: int = 0, model_id: Optio
 
 
 def random_prompt(vocab_size: int, n: int, seed: int = 1234) -> np.ndarray:
-    """Token ids uniform in [0, vocab) — SURVEY.md section 8(d) 'synthetic prompts'."""
+    """Token ids uniform in [0, vocab): synthetic prompts."""
     return np.random.Generator(np.random.SFC64(seed)).integers(0, vocab_size, size=n, dtype=np.int32)

@@ -168,6 +168,6 @@ GGUF_PY_CASES = [("Q4_K", L.Q4_K, 256, 24, 4, 101, 1.0), ("Q4_K", L.Q4_K, 256, 3
                  ("Q4_0", L.Q4_0, 32, 24, 16, 104, 1.0), ("Q8_0", L.Q8_0, 32, 24, 16, 105, 1.0), ("Q8_0", L.Q8_0, 32, 5, 152, 106, 30.0),
                  ("Q5_K", L.Q5_K, 256, 24, 4, 107, 1.0), ("Q5_K", L.Q5_K, 256, 3, 56, 108, 0.02)]
 # Q5_K dot products (real-file coverage): (K, rows, seed) - golden values from the compiled reference's ggml_vec_dot_q5_K_q8_K
-# (tests/golden/make_golden_q5k.py -> q5k_dot.npz); the reference's DataType layer cannot carry Q5_K (SURVEY F1), so its operator
+# (tests/golden/make_golden_q5k.py -> q5k_dot.npz); the reference's DataType layer cannot carry Q5_K, so its operator
 # table is not involved
 Q5K_DOT_CASES = [(256, 9, 201), (256 * 16, 7, 202), (256 * 56, 5, 203)]

@@ -1,6 +1,6 @@
 """Golden vectors from the reference's OWN known-answer machinery for the hot path's data formats: the Python
 `gguf.quants.dequantize` of /root/reference/tools/convert_hf_to_gguf/gguf-py, which the reference's
-gguf-py/tests/test_quants.py:187-262 pins bit-exact against libggml's dequantize_row_* (SURVEY section 4).  The Python
+gguf-py/tests/test_quants.py:187-262 pins bit-exact against libggml's dequantize_row_*.  The Python
 reference cannot travel to the GPU box, so its outputs on seeded blocks are committed here.
 Run in the build container:  python tests/golden/make_golden_gguf_py.py   ->  tests/golden/gguf_py.npz
 Inputs are regenerated from the seeds by the test (powerserve_b200.synth.random_blocks is deterministic)."""

@@ -2,7 +2,7 @@
 Platform) built with the CUDABackend of powerserve_b200/host plugged in must produce the same logits
 and greedy ids as the reference's CPU path — checked against the committed golden vectors of the compiled reference and,
 for the fused decode path, against the oracle.  Needs powerserve_b200/host/_build/ps_cuda_run (built where
-/root/reference exists; the binary travels with gpurun)."""
+/root/reference exists; the binary travels with the tree)."""
 import json
 import os
 import subprocess
@@ -77,7 +77,7 @@ def test_powerserve_unfused_graph_op_by_op_on_cuda_matches_reference_golden(pres
 @needs_exe
 @pytest.mark.parametrize("preset,n_prompt,batch,n_dec", cases.MODEL_CASES[:3])
 def test_powerserve_stack_with_device_side_topk(preset, n_prompt, batch, n_dec):
-    """SURVEY 8 f3: the stack with lazy logits - CUDA_FORWARD leaves the logits on the device, CUDABackend::topk runs TopKSampler
+    """Device-side sampling: the stack with lazy logits - CUDA_FORWARD leaves the logits on the device, CUDABackend::topk runs TopKSampler
     there and the host picks from 40 (logit, token) pairs; the greedy ids must be the golden ones."""
     gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "models.npz"))
     prompt = synth.random_prompt(synth.PRESETS[preset].vocab_size, n_prompt, seed=7 + n_prompt)

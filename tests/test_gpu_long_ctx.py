@@ -1,4 +1,4 @@
-"""GPU parity at the BENCHMARKED context length and beyond (VERDICT r01 "parity holes"): 2100- and 4400-token prompts
+"""GPU parity at the BENCHMARKED context length and beyond: 2100- and 4400-token prompts
 (tcgen05 prefill GEMM in chunks of 128, batched attention) followed by fused / graph-replayed decode steps, on the real
 per-layer shapes of Llama-3.1-8B and Llama-3.2-1B, against the committed golden vectors of the compiled reference
 (tests/golden/long_ctx.npz) — bit for bit.  n_ctx = 4096 is the bench configuration; n_ctx = 8192 puts the decode

@@ -9,7 +9,7 @@ from tests import _libs as L
 
 pytestmark = pytest.mark.gpu
 
-QTYPES = [(L.Q4_K, 256), (L.Q6_K, 256), (L.Q4_0, 32), (L.Q8_0, 32), (L.Q5_K, 256)]   # Q5_K: real-file coverage (SURVEY 8 f2)
+QTYPES = [(L.Q4_K, 256), (L.Q6_K, 256), (L.Q4_0, 32), (L.Q8_0, 32), (L.Q5_K, 256)]   # Q5_K: real-file coverage
 
 
 @pytest.fixture(scope="module")
@@ -57,7 +57,7 @@ def test_matmul_bit_exact(be, t, blk, bs, kind):
 
 
 def test_matmul_real_shapes_q4k(be):
-    """Llama-3.1-8B / 3.2-1B shapes (SURVEY section 8): sampled rows only on the oracle side to stay fast."""
+    """Llama-3.1-8B / 3.2-1B shapes: sampled rows only on the oracle side to stay fast."""
     o = L.oracle()
     rng = np.random.default_rng(7)
     for K, N in [(4096, 4096), (4096, 1024), (14336, 4096), (2048, 8192)]:
@@ -214,7 +214,7 @@ def test_get_embedding_f16_table(be):
 
 def test_rope_freq_factors(be):
     """rope_freqs.weight (ggml_rope_cache_init with freq_factors, ggml.c:15342-15356: rope_yarn(theta / ff, ...)); off by default
-    because the reference never passes it (SURVEY F6).  Checked against a float32 restatement evaluated with the platform
+    because the reference never passes it.  Checked against a float32 restatement evaluated with the platform
     libm (the table is built on the host with cosf / sinf / powf), then switched off again (bit-exact vs the oracle)."""
     import ctypes as C
     libm = C.CDLL("libm.so.6")

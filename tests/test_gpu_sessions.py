@@ -1,4 +1,4 @@
-"""Server-side batching (SURVEY section 8 f4): several independent sessions (KV sets) over one set of weights, advanced one token
+"""Server-side batching: several independent sessions (KV sets) over one set of weights, advanced one token
 each per forward pass - one weight stream for the whole batch, attention per column over its own cache.  Parity: every
 session's logits are bit-identical to decoding that sequence alone with batch 1 (and hence to the oracle, which the
 single-sequence tests pin)."""

@@ -1,8 +1,8 @@
-"""Speculative decoding on the CUDA backend (BASELINE configs[3]): the KVCacheInterface slot
+"""Speculative decoding on the CUDA backend: the KVCacheInterface slot
 operations, the tree forward, and the token-tree loop (include/ps_spec.h) - whose output must be the target model's own
 greedy continuation.
 
-The reference cannot pin this path (its CPU backend ignores tree masks, SURVEY F7; the QNN backend that implements it
+The reference cannot pin this path (its CPU backend ignores tree masks; the QNN backend that implements it
 does not run here), so parity is pinned by (a) bit-equality of a causal tree batch with the plain forward, (b) a dense
 fp32 restatement of the masked attention semantics (src/backend/qnn/causal_models.cpp:215-230) through path equivalence:
 a node's logits equal those of the plain causal run over root..node, and (c) the lossless invariant."""
@@ -112,7 +112,7 @@ def test_tree_batch_path_equivalence_and_slot_ops():
 
 
 def _chunking_noise(path, prompt, vocab):
-    """The reference-vs-reference yardstick (SURVEY F13): logits of the SAME 12 tokens fed as one batch and one by one.
+    """The reference-vs-reference yardstick: logits of the SAME 12 tokens fed as one batch and one by one.
     Both runs are bit-identical to the ggml CPU reference (tests/test_gpu_model.py) and still differ, because its soft-max
     row length - and with it the hand-over from the SIMD exp to libm expf - depends on the chunking, and activation
     re-quantisation amplifies the ulp-level difference layer by layer."""

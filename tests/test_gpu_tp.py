@@ -1,7 +1,7 @@
-"""Tensor parallelism (SURVEY section 8e) on real GPUs: N processes, one per GPU, row-sharded weights, NCCL all-gathers
+"""Tensor parallelism on real GPUs: N processes, one per GPU, row-sharded weights, NCCL all-gathers
 inside the decode graph (mode nccl) or fused into the producing kernels as NVLink peer stores + epoch flags (mode p2p).
 Row sharding keeps every dot product whole, so the result must be BIT-IDENTICAL to one GPU —
-checked against the oracle.  Needs >= 2 GPUs (skipped otherwise; run with `gpurun --gpus 2`)."""
+checked against the oracle.  Needs >= 2 GPUs (skipped otherwise; run on a box with two GPUs)."""
 import os
 import subprocess
 import sys

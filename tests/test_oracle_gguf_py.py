@@ -1,6 +1,5 @@
 """The oracle's block de-quantisers against the reference's own known-answer machinery for the hot path's data formats:
-`gguf.quants.dequantize` of the reference's gguf-py, which its tests/test_quants.py pins bit-exact against libggml
-(SURVEY section 4).  The Python reference's outputs on seeded blocks are committed in tests/golden/gguf_py.npz
+`gguf.quants.dequantize` of the reference's gguf-py, which its tests/test_quants.py pins bit-exact against libggml.  The Python reference's outputs on seeded blocks are committed in tests/golden/gguf_py.npz
 (generator: tests/golden/make_golden_gguf_py.py); get_embedding is the operator of the path that de-quantises rows
 (ggml_wrapper.cpp:181-211 -> dequantize_row_q4_0 / q8_0 / q4_K / q6_K)."""
 import os

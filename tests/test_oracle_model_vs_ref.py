@@ -27,7 +27,7 @@ def test_logits_and_ids_bit_exact(preset, n_prompt, batch):
 
 
 def test_reference_is_thread_count_invariant():
-    """every output element is one thread's vec_dot, so 1 vs 5 threads give identical logits."""
+    """Every output element is one thread's vec_dot, so 1 vs 5 threads give identical logits."""
     d = M.model_dir("tiny-llama")
     prompt = synth.random_prompt(1024, 17)
     a = M.run_reference(d, prompt, 4, n_threads=1, dump_logits=4)

@@ -13,7 +13,7 @@ from tests import _libs as L
 pytestmark = pytest.mark.skipif(not L.have_ref(), reason="oracle/_ref not built (needs /root/reference)")
 
 QTYPES = [(L.Q4_K, 256), (L.Q6_K, 256), (L.Q4_0, 32), (L.Q8_0, 32)]
-# Q5_K (real Q4_K_S / Q5_K_M files): pinned at the block level - the reference's own DataType layer cannot carry it (SURVEY F1)
+# Q5_K (real Q4_K_S / Q5_K_M files): pinned at the block level - the reference's own DataType layer cannot carry it
 BLOCK_TYPES = QTYPES + [(L.Q5_K, 256)]
 
 

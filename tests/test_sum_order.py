@@ -1,4 +1,4 @@
-"""DESIGN.md section 2, last bullet: the CUDA kernels add the double-precision sums of RMSNorm in a tree order (lane
+"""The CUDA kernels add the double-precision sums of RMSNorm in a tree order (lane
 partials -> warp butterfly -> warps) while the reference adds sequentially (ggml.c:12691-12697).  The doubles differ in
 their last bits; the claim is that the ONE fp32 value derived from them (the norm scale) does not.  This test pins the
 claim on CPU with a numpy model of the kernel's order (ps_rw.cuh prologue) against the sequential order."""

@@ -1,4 +1,4 @@
-"""The arithmetic claim behind the tcgen05 prefill GEMM (powerserve_b200/csrc/ps_tc.cuh, DESIGN.md section 5): the integer
+"""The arithmetic claim behind the tcgen05 prefill GEMM (powerserve_b200/csrc/ps_tc.cuh): the integer
 lane sums of ggml_vec_dot_q4_K_q8_K are EXACT when computed as an fp16 x fp16 -> fp32 contraction, in any accumulation
 order - every operand is an integer fp16 represents exactly, every product is exact in fp32, and every partial sum stays
 below 2^24.  Pinned here on CPU with numpy (no GPU needed): worst-case bounds and random data in shuffled orders."""
