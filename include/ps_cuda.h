@@ -209,18 +209,37 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
 
 /* ---------------------------------------------------------------------------------------------- layer-list models
  * Models that a configuration file describes layer by layer (config.json + model.safetensors, weights in bfloat16)
- * instead of the fixed llama / qwen2 stack above.  A layer is a token mixer plus an optional feed-forward, both reading
- * ONE norm's output ("parallel block"): x <- x + (mixer(N(x)) + ff(N(x))).  Every mechanism is a parameter set of its
- * own, so that another design can combine them differently:
+ * instead of the fixed llama / qwen2 stack above.  A layer is a token mixer plus an optional feed-forward.
+ *   block_kind PS_BLOCK_PARALLEL: both read ONE norm's output, x <- x + (mixer(N(x)) + ff(N(x)));
+ *   block_kind PS_BLOCK_SEQUENTIAL: x <- x + P1(mixer(N1(x))), then x <- x + P2(ff(N2(x))); P1 / P2 are norms of the
+ *   sublayer's OUTPUT when post_norm = 1, the identity otherwise.
+ * Every mechanism is a parameter set of its own, so that another design can combine them differently:
  *   attention  - grouped-query, separate query/key and value head sizes, projection biases, no rotation;
- *                score = q.k * score_scale [* head_temp[h]] [+ rel[bucket(i - j)][h]] [mixed over heads by head_mix],
- *                soft-max with an optional sink (one more term exp(0) in the denominator that carries no value);
- *                bucket(n) = n below rel_buckets / 2, then logarithmic up to rel_max_dist (last bucket beyond).
+ *                qk_norm = 1: every head's q and k are divided by their root mean square (no weight, eps = norm_eps);
+ *                score = q.k * score_scale [* head_temp[h]] [+ rel[bucket(i - j)][h]] [- r1[h] ln(1 + r2[h] (i - j))]
+ *                [mixed over heads by head_mix]; window > 0: query i sees the keys i - window < j <= i only;
+ *                soft-max with an optional sink (one more term in the denominator that carries no value: exp(0) for
+ *                sink = PS_SINK_ZERO, exp(sink[h]) for PS_SINK_LEARNED);
+ *                bucket(n) = n below rel_buckets / 2, then logarithmic up to rel_max_dist (last bucket beyond);
+ *                v_mix: PS_VMIX_SOURCE keeps the layer's value rows of the tokens in flight, PS_VMIX_BLEND replaces
+ *                v by (1 - vmix) v + vmix v_source before it is cached (same value width in both layers).
+ *   latent attention - queries through a normed latent (c_q = N(W_dq h; dq_norm), q = W_uq c_q, per head qk_dim plain
+ *                + rot_dim rotated dims); W_dkv h gives kv_rank latent dims (normed with dkv_norm: the latent c) and
+ *                rot_dim dims of ONE rotated key part shared by all heads; per head k = W_uk c, v = W_uv c;
+ *                score = (q_plain . k + q_rot . k_rot) * score_scale, causal or windowed, sink as above.  The cache
+ *                holds c and the rotated key part only: the executor folds W_uk into the query and applies W_uv to
+ *                the weighted sum of latents.
+ *   rotation   - the first rope_dims dims of a rotated vector, pairs (i, i + rope_dims / 2), angle pos * f_i with
+ *                f_i = rope_base^(-2 i / rope_dims); rope_factor > 0 adds YaRN: f_i <- f_i / factor * ramp_i +
+ *                f_i (1 - ramp_i) with the ramp between the dims whose wavelength fits rope_original positions
+ *                rope_fast and rope_slow times, and cos / sin scaled by 0.1 ln(factor) + 1.
+ *   dense ff   - PS_MLP_DENSE: one gated feed-forward of expert_ff rows with the expert's activation below.
  *   routed ff  - n_experts gated experts, the top_k largest router scores choose; router_act 1 = sigmoid scores;
  *                route_on_input = 1: the score multiplies the expert's INPUT; route_renorm = 1: the chosen scores are
  *                divided by their sum.  Expert: g = min(Wg z, act_limit), u = clamp(Wu z, +-act_limit),
  *                y = g * sigmoid(act_alpha * g) * (u + up_shift), out = Wd y.
- *   norm       - RMS norm with eps inside the root; norm_unit_offset = 1: the stored weight is around zero (1 + w).
+ *   norm       - RMS norm with eps inside the root; norm_unit_offset = 1: the stored weight is around zero (1 + w);
+ *                norm_groups > 1: the vector is cut into that many equal parts, each divided by its own root mean square.
  * The context made by ps_cuda_create_arch is an ordinary ps_cuda_ctx: ps_cuda_forward, ps_cuda_decode_greedy,
  * ps_cuda_sample_topk, ps_cuda_logits_dev, the ps_cuda_kv_* position calls and the ps_cuda_session_* calls work on it
  * as on a llama context (the per-layer cache rows have the layer's own widths; V is kept transposed like there).  The
@@ -229,8 +248,11 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  * compute = PS_COMPUTE_BF16: matrix products take bfloat16 operands and accumulate in fp32; the residual stream, norms,
  * attention scores / weights, routers and the cache stay fp32.  PS_COMPUTE_F32: every product in true fp32 (FMA). */
 enum ps_cuda_compute { PS_COMPUTE_BF16 = 0, PS_COMPUTE_F32 = 1 };
-enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1 };
-enum ps_cuda_mlp_kind { PS_MLP_NONE = 0, PS_MLP_ROUTED = 1 };
+enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1, PS_MIXER_LATENT = 2 };
+enum ps_cuda_mlp_kind { PS_MLP_NONE = 0, PS_MLP_ROUTED = 1, PS_MLP_DENSE = 2 };
+enum ps_cuda_block_kind { PS_BLOCK_PARALLEL = 0, PS_BLOCK_SEQUENTIAL = 1 };
+enum ps_cuda_sink_kind { PS_SINK_NONE = 0, PS_SINK_ZERO = 1, PS_SINK_LEARNED = 2 };
+enum ps_cuda_vmix_kind { PS_VMIX_NONE = 0, PS_VMIX_SOURCE = 1, PS_VMIX_BLEND = 2 };
 
 typedef struct {
     int32_t mixer_kind;
@@ -240,12 +262,21 @@ typedef struct {
     int32_t head_temp;                  /* per-head score multiplier */
     int32_t rel_buckets; float rel_max_dist; /* rows of the distance-bias table (0 = none) and the distance of its last bucket */
     int32_t head_mix;                   /* [H][H] mixing of the heads' scores before the soft-max */
-    int32_t sink;                       /* soft-max denominator has one more term of score 0 */
+    int32_t sink;                       /* enum ps_cuda_sink_kind: one more term in the soft-max denominator */
     int32_t mlp_kind;
     int32_t n_experts, top_k, expert_ff;
     int32_t router_act;                 /* 1 = sigmoid */
     int32_t route_on_input, route_renorm;
     float   act_limit, act_alpha, up_shift;
+    int32_t block_kind;                 /* enum ps_cuda_block_kind */
+    int32_t post_norm;                  /* sequential blocks: every sublayer's output is normed before the residual add */
+    int32_t qk_norm;                    /* q and k divided by their root mean square per head */
+    int32_t window;                     /* > 0: keys further back than window - 1 positions are not seen */
+    int32_t log_bias;                   /* score -= r1[h] * ln(1 + r2[h] * distance) */
+    int32_t v_mix;                      /* enum ps_cuda_vmix_kind */
+    int32_t q_rank, kv_rank, rot_dim;   /* latent attention */
+    int32_t rope_dims, rope_original;   /* rotation: rotated dims; YaRN's original context */
+    float   rope_base, rope_factor, rope_fast, rope_slow; /* rope_factor = 0: plain rotation */
 } ps_cuda_layer_desc;
 
 typedef struct {
@@ -255,12 +286,17 @@ typedef struct {
     int32_t norm_unit_offset;
     int32_t compute;                    /* enum ps_cuda_compute */
     const ps_cuda_layer_desc *layers;   /* n_layers entries */
+    int32_t norm_groups;                /* 0 or 1: one group */
 } ps_cuda_arch_desc;
 
 /* matrices [out][in] in bfloat16; vectors and the small tables in bfloat16 or fp32 */
 typedef struct {
     ps_cuda_tensor norm, q, q_bias, k, k_bias, v, v_bias, o, o_bias, rel, head_mix, head_temp, router;
-    const ps_cuda_tensor *gate, *up, *down; /* n_experts entries each (NULL without a feed-forward) */
+    const ps_cuda_tensor *gate, *up, *down; /* n_experts entries each, one for a dense feed-forward (NULL without a feed-forward) */
+    /* sequential blocks: norm of the mixer's output, norm before the feed-forward, norm of its output */
+    ps_cuda_tensor norm_mix_out, norm_ff, norm_ff_out;
+    ps_cuda_tensor r1, r2, sink, vmix;  /* [H], [H], [H], scalar */
+    ps_cuda_tensor dq, dq_norm, uq, dkv, dkv_norm, uk, uv; /* latent attention */
 } ps_cuda_arch_layer_weights;
 
 typedef struct {

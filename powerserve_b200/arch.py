@@ -37,7 +37,7 @@ class LayerListModel(capi.CudaModel):
         layers, top = describe(cfg, self.tensors)
         self._layer_descs = (LayerDesc * len(layers))(*layers)
         self.desc = ArchDesc(top["dim"], top["vocab_size"], len(layers), int(n_ctx), int(max_batch), top["norm_eps"], top["embed_scale"],
-                             top["norm_unit_offset"], compute, self._layer_descs)
+                             top["norm_unit_offset"], compute, self._layer_descs, int(top.get("norm_groups", 1)))
         self.vocab = self.desc.vocab_size
         self.be = capi.CudaBackend(self.desc, device)
 
@@ -54,7 +54,7 @@ class LayerListModel(capi.CudaModel):
         self._lw = (ArchLayerWeights * len(layers))()
         for i, ln in enumerate(names["layers"]):
             lw = ArchLayerWeights()
-            for f in ("norm", "q", "q_bias", "k", "k_bias", "v", "v_bias", "o", "o_bias", "rel", "head_mix", "head_temp", "router"):
+            for f in ("norm", "q", "q_bias", "k", "k_bias", "v", "v_bias", "o", "o_bias", "rel", "head_mix", "head_temp", "router") + capi.ARCH_LAYER_VECTORS_2:
                 setattr(lw, f, T(ln.get(f)))
             for f in ("gate", "up", "down"):
                 lst = ln.get(f)
@@ -125,8 +125,85 @@ def _nufusun_tensor_names(cfg: dict) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------------------------------------ Vanapel
+# Decoder-only; every layer is a sequential block whose sublayers are normed on the way in AND on the way out,
+#   x <- x + N1b(mixer(N1(x))),  x <- x + N2b(ff(N2(x))),
+# with RMS norms taken over `norm.groups` equal parts of the vector.  Two mixers, chosen per layer by "type":
+#   "attention"         grouped-query, no rotation and no biases; q and k of every head scaled to unit RMS; the score loses
+#                       r1_h ln(1 + r2_h (i - j)) with distance; a sliding window of mask.size keys; a learned per-head sink
+#                       logit in the soft-max denominator; layers marked v_mix blend their values with those of the FIRST marked
+#                       layer (weight '.vmix'; the first one's own is unused).
+#   "latent_attention"  queries through a normed latent, keys / values up-projected from a shared normed latent plus one
+#                       rotated key part common to all heads (rotate-half pairs, YaRN-scaled frequencies); causal; learned sink.
+# Feed-forward: one gated unit, y = g sigmoid(1.702 g) (u + 1) on g = min(gate, limit), u = clamp(up, +-limit).
+def _vanapel_describe(cfg: dict, tensors) -> Tuple[List[LayerDesc], dict]:
+    layers = []
+    v_source_seen = False
+    for i, l in enumerate(cfg["layers"]):
+        m = l["mixer"]
+        d = LayerDesc()
+        d.block_kind, d.post_norm = capi.BLOCK_SEQUENTIAL, 1
+        d.n_heads, d.qk_dim, d.v_dim = m["heads"], m["dim"], m["vdim"]
+        d.score_scale = m["scale"]
+        d.sink = capi.SINK_LEARNED
+        if l["type"] == "attention":
+            d.mixer_kind = capi.MIXER_ATTENTION
+            d.n_kv_heads = m["kv_heads"]
+            d.qk_norm, d.log_bias = 1, 1
+            d.window = int((m.get("mask") or {}).get("size", 0))
+            if m.get("v_mix"):
+                d.v_mix = capi.VMIX_BLEND if v_source_seen else capi.VMIX_SOURCE
+                v_source_seen = True
+        elif l["type"] == "latent_attention":
+            d.mixer_kind = capi.MIXER_LATENT
+            d.n_kv_heads = 1
+            d.q_rank, d.kv_rank, d.rot_dim = m["q_rank"], m["kv_rank"], m["rot_dim"]
+            rot = m.get("rot") or {}
+            d.rope_dims, d.rope_base = int(rot.get("dims", d.rot_dim)), float(rot.get("base", 10000.0))
+            sc = rot.get("scaling")
+            if sc:
+                d.rope_factor, d.rope_original, d.rope_fast, d.rope_slow = float(sc["factor"]), int(sc["original"]), float(sc["fast"]), float(sc["slow"])
+            d.window = int((m.get("mask") or {}).get("size", 0))
+        else:
+            raise capi.PsCudaError(f"Vanapel layer {i}: unknown mixer type {l['type']!r}")
+        mlp = l.get("mlp")
+        if mlp is None:
+            d.mlp_kind = capi.MLP_NONE
+        elif mlp.get("kind") == "dense":
+            d.mlp_kind = capi.MLP_DENSE
+            d.expert_ff, d.act_limit = mlp["ff"], mlp["limit"]
+            d.act_alpha, d.up_shift = 1.702, 1.0
+        else:
+            raise capi.PsCudaError(f"Vanapel layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(d)
+    top = {"dim": cfg["width"], "vocab_size": cfg["vocab"], "norm_eps": cfg["norm"]["eps"], "embed_scale": 1.0, "norm_unit_offset": 0,
+           "norm_groups": int(cfg["norm"].get("groups", 1))}
+    return layers, top
+
+
+def _vanapel_tensor_names(cfg: dict) -> dict:
+    out = {"embed": "embed", "final_norm": "final.norm", "head": "head", "layers": []}
+    for i, l in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        n = {"norm": p + "norm1", "norm_mix_out": p + "norm1b", "o": p + "mix.o", "sink": p + "mix.sink"}
+        if l["type"] == "attention":
+            n.update({"q": p + "mix.q", "k": p + "mix.k", "v": p + "mix.v", "r1": p + "mix.r1", "r2": p + "mix.r2"})
+            if l["mixer"].get("v_mix"):
+                n["vmix"] = p + "mix.vmix"
+        else:
+            n.update({"dq": p + "mix.dq", "dq_norm": p + "mix.dq.norm", "uq": p + "mix.uq", "dkv": p + "mix.dkv", "dkv_norm": p + "mix.dkv.norm",
+                      "uk": p + "mix.uk", "uv": p + "mix.uv"})
+        if l.get("mlp") is not None:
+            n.update({"norm_ff": p + "norm2", "norm_ff_out": p + "norm2b"})
+            for f in ("gate", "up", "down"):
+                n[f] = [f"{p}mlp.{f}"]
+        out["layers"].append(n)
+    return out
+
+
 ARCHITECTURES: Dict[str, Tuple[Callable, Callable]] = {
     "Nufusun": (_nufusun_describe, _nufusun_tensor_names),
+    "Vanapel": (_vanapel_describe, _vanapel_tensor_names),
 }
 
 

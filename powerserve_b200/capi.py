@@ -49,18 +49,26 @@ class LayerDesc(C.Structure):
                 ("score_scale", C.c_float), ("proj_bias", C.c_int32), ("head_temp", C.c_int32), ("rel_buckets", C.c_int32), ("rel_max_dist", C.c_float),
                 ("head_mix", C.c_int32), ("sink", C.c_int32), ("mlp_kind", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32),
                 ("expert_ff", C.c_int32), ("router_act", C.c_int32), ("route_on_input", C.c_int32), ("route_renorm", C.c_int32),
-                ("act_limit", C.c_float), ("act_alpha", C.c_float), ("up_shift", C.c_float)]
+                ("act_limit", C.c_float), ("act_alpha", C.c_float), ("up_shift", C.c_float),
+                ("block_kind", C.c_int32), ("post_norm", C.c_int32), ("qk_norm", C.c_int32), ("window", C.c_int32), ("log_bias", C.c_int32),
+                ("v_mix", C.c_int32), ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rope_dims", C.c_int32),
+                ("rope_original", C.c_int32), ("rope_base", C.c_float), ("rope_factor", C.c_float), ("rope_fast", C.c_float), ("rope_slow", C.c_float)]
 
 
 class ArchDesc(C.Structure):
     _fields_ = [("dim", C.c_int32), ("vocab_size", C.c_int32), ("n_layers", C.c_int32), ("n_ctx", C.c_int32), ("max_batch", C.c_int32),
                 ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("norm_unit_offset", C.c_int32), ("compute", C.c_int32),
-                ("layers", C.POINTER(LayerDesc))]
+                ("layers", C.POINTER(LayerDesc)), ("norm_groups", C.c_int32)]
+
+
+# the layer tensors after the expert lists, in the order of ps_cuda_arch_layer_weights
+ARCH_LAYER_VECTORS_2 = ("norm_mix_out", "norm_ff", "norm_ff_out", "r1", "r2", "sink", "vmix", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv")
 
 
 class ArchLayerWeights(C.Structure):
     _fields_ = [(n, Tensor) for n in ("norm", "q", "q_bias", "k", "k_bias", "v", "v_bias", "o", "o_bias", "rel", "head_mix", "head_temp", "router")] + \
-               [("gate", C.POINTER(Tensor)), ("up", C.POINTER(Tensor)), ("down", C.POINTER(Tensor))]
+               [("gate", C.POINTER(Tensor)), ("up", C.POINTER(Tensor)), ("down", C.POINTER(Tensor))] + \
+               [(n, Tensor) for n in ARCH_LAYER_VECTORS_2]
 
 
 class ArchWeights(C.Structure):
@@ -69,6 +77,10 @@ class ArchWeights(C.Structure):
 
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 MIXER_ATTENTION, MLP_NONE, MLP_ROUTED = 1, 0, 1
+MIXER_LATENT, MLP_DENSE = 2, 2
+BLOCK_PARALLEL, BLOCK_SEQUENTIAL = 0, 1
+SINK_NONE, SINK_ZERO, SINK_LEARNED = 0, 1, 2
+VMIX_NONE, VMIX_SOURCE, VMIX_BLEND = 0, 1, 2
 
 _lib: Optional[C.CDLL] = None
 

@@ -32,6 +32,17 @@ struct PsArchLayer {
     uint16_t *bucket = nullptr; // distance -> row of the bias table, n_ctx entries
     // tensor-core operand blocks of the matrices (bfloat16 compute only): q|k|v, o, gate, up, down (per expert)
     uint8_t *t_qkv = nullptr, *t_o = nullptr, *t_gate = nullptr, *t_up = nullptr, *t_down = nullptr;
+    // sequential blocks: norm of the mixer's output, norm before the feed-forward, norm of its output
+    float *norm_mix_out = nullptr, *norm_ff = nullptr, *norm_ff_out = nullptr;
+    float *r1 = nullptr, *r2 = nullptr, *sink_v = nullptr, *vmix = nullptr;
+    // latent attention: wqkv holds W_dq | W_dkv (pw rows); W_uq; W_uk transposed per head [H][kv_rank][qk_dim] (folded into the query);
+    // W_uv per head [H][v_dim][kv_rank] (applied to the weighted sum of latents)
+    int pw = 0;      // rows of the first projection (q|k|v, or q latent | kv latent | rotated key part)
+    int aw = 0;      // width of the attention output rows (H * v_dim, or H * kv_rank before W_uv)
+    bf16 *wuq = nullptr, *wukt = nullptr, *wuv = nullptr;
+    float *dq_norm = nullptr, *dkv_norm = nullptr, *rope_freq = nullptr;
+    float rope_mscale = 1.0f;
+    uint8_t *t_uq = nullptr;
 };
 
 struct PsArch {
@@ -47,6 +58,10 @@ struct PsArch {
     int *sel_e = nullptr, *row_token = nullptr, *row_slot = nullptr, *tile_e = nullptr, *tile_row0 = nullptr, *tile_end = nullptr, *n_tiles = nullptr;
     float *z = nullptr;    // router logits of the single-token step
     float *pm = nullptr, *pl = nullptr; // per-block soft-max statistics of the single-token step
+    float *cq = nullptr, *lq = nullptr, *qa = nullptr, *att2 = nullptr; // latent attention: normed query latent, queries, queries with W_uk folded in, values after W_uv
+    float *vsrc = nullptr; // value rows of the tokens in flight from the layer others blend theirs with
+    float *x2 = nullptr;   // second residual buffer of the single-token step of sequential blocks
+    int max_rq = 0, max_lq = 0, max_qa = 0, max_att2 = 0, vsrc_w = 0;
     int ldP = 0;
     int64_t ldS = 0;
     int max_qkv = 0, max_od = 0, max_h = 0, max_top = 0, max_ff = 0, max_e = 0, max_dv = 0;
@@ -64,6 +79,7 @@ struct PsArch {
     int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, four for long streams or without overlap)
     int opt_prefetch = 1; // 1: a mat-vec CTA requests its first row group into L2 before the dependency wait; 2: every next group too
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
+    bool has_seq = false; // some layer is a sequential block
 };
 
 namespace {
@@ -195,6 +211,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     if (d.dim <= 0 || d.vocab_size <= 0 || d.n_layers <= 0 || d.n_ctx <= 0 || d.max_batch <= 0 || !d.layers)
         return afail(err, PS_CUDA_ERR_INVALID, "layer-list descriptor has non-positive fields");
     if (d.compute != PS_COMPUTE_BF16 && d.compute != PS_COMPUTE_F32) return afail(err, PS_CUDA_ERR_INVALID, "unknown compute mode %d", d.compute);
+    if (d.norm_groups < 0 || (d.norm_groups > 1 && d.dim % d.norm_groups)) return afail(err, PS_CUDA_ERR_INVALID, "width %d does not split into %d norm groups", d.dim, d.norm_groups);
     PsArch *a = new PsArch();
     a->d = d;
     a->round = d.compute == PS_COMPUTE_BF16;
@@ -204,24 +221,57 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         const ps_cuda_layer_desc &l = d.layers[i];
         PsArchLayer &w = a->L[(size_t)i];
         w.d = l;
-        if (l.mixer_kind != PS_MIXER_ATTENTION) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
+        if (l.block_kind == PS_BLOCK_SEQUENTIAL) a->has_seq = true;
+        if (l.mixer_kind != PS_MIXER_ATTENTION && l.mixer_kind != PS_MIXER_LATENT) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
+        const bool latent = l.mixer_kind == PS_MIXER_LATENT;
+        if (latent && (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) ||
+                       l.n_kv_heads != 1 || l.proj_bias || l.head_temp || l.head_mix || l.rel_buckets || l.qk_norm || l.v_mix || l.block_kind != PS_BLOCK_SEQUENTIAL))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported latent attention (ranks %d / %d, %d rotated dims of which %d rotate)", i, l.q_rank, l.kv_rank, l.rot_dim, l.rope_dims));
+        if (l.block_kind != PS_BLOCK_PARALLEL && l.block_kind != PS_BLOCK_SEQUENTIAL) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown block kind %d", i, l.block_kind));
+        if (l.block_kind == PS_BLOCK_PARALLEL && (l.post_norm || l.qk_norm || l.v_mix || l.mlp_kind == PS_MLP_DENSE))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: output norms, unit-RMS q / k, value blending and the dense feed-forward need a sequential block", i));
+        if (l.block_kind == PS_BLOCK_SEQUENTIAL && (l.mlp_kind == PS_MLP_ROUTED || l.proj_bias || l.head_mix || l.head_temp || l.rel_buckets))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: routed experts, projection biases, head mixing / temperatures and the bias table need a parallel block", i));
+        if (l.window < 0 || l.sink < PS_SINK_NONE || l.sink > PS_SINK_LEARNED || l.v_mix < PS_VMIX_NONE || l.v_mix > PS_VMIX_BLEND)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: window %d, sink kind %d, value blending %d", i, l.window, l.sink, l.v_mix));
         if (l.n_heads <= 0 || l.n_kv_heads <= 0 || l.n_heads % l.n_kv_heads || l.qk_dim <= 0 || l.v_dim <= 0 || l.n_heads > PA_MAX_HEADS)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported head geometry (%d / %d heads, sizes %d / %d; at most %d heads)", i, l.n_heads,
                               l.n_kv_heads, l.qk_dim, l.v_dim, PA_MAX_HEADS));
         if (l.rel_buckets < 0 || l.rel_buckets > 65535 || (l.rel_buckets > 0 && (l.rel_buckets < 2 || !(l.rel_max_dist > (float)(l.rel_buckets / 2)))))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: distance-bias table of %d rows up to distance %g", i, l.rel_buckets, (double)l.rel_max_dist));
-        if (l.mlp_kind != PS_MLP_NONE && l.mlp_kind != PS_MLP_ROUTED) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown feed-forward kind %d", i, l.mlp_kind));
+        if (l.mlp_kind != PS_MLP_NONE && l.mlp_kind != PS_MLP_ROUTED && l.mlp_kind != PS_MLP_DENSE) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown feed-forward kind %d", i, l.mlp_kind));
         if (l.mlp_kind == PS_MLP_ROUTED && (l.n_experts <= 0 || l.n_experts > PA_MAX_EXPERTS || l.top_k <= 0 || l.top_k > l.n_experts || l.expert_ff <= 0 || l.router_act != 1))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported routed feed-forward (%d experts, top %d, ff %d, router activation %d)", i, l.n_experts,
                               l.top_k, l.expert_ff, l.router_act));
-        if (pa_dec_scores_smem(l.n_heads, l.n_kv_heads, l.qk_dim) > 160 * 1024 || (size_t)d.dim * 4 > 160 * 1024)
-            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of size %d (or width %d) exceed the single-token kernels' shared memory", i, l.n_heads, l.qk_dim, d.dim));
-        w.qd = l.n_heads * l.qk_dim; w.kd = l.n_kv_heads * l.qk_dim; w.vd = l.n_kv_heads * l.v_dim; w.od = l.n_heads * l.v_dim;
-        a->max_qkv = std::max(a->max_qkv, w.qd + w.kd + w.vd);
-        a->max_od = std::max(a->max_od, w.od);
+        if (l.mlp_kind == PS_MLP_DENSE && l.expert_ff <= 0) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: dense feed-forward of %d rows", i, l.expert_ff));
+        // the attention kernels see a latent layer as one shared key head of kv_rank + rot_dim dims whose values are the latents
+        const int a_dq = latent ? l.kv_rank + l.rot_dim : l.qk_dim, a_dv = latent ? l.kv_rank : l.v_dim;
+        if (pa_dec_scores_smem(l.n_heads, l.n_kv_heads, a_dq) > 160 * 1024 || (size_t)d.dim * 4 > 160 * 1024)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of size %d (or width %d) exceed the single-token kernels' shared memory", i, l.n_heads, a_dq, d.dim));
+        w.qd = l.n_heads * a_dq; w.kd = l.n_kv_heads * a_dq; w.vd = l.n_kv_heads * a_dv; w.od = l.n_heads * l.v_dim;
+        w.pw = latent ? l.q_rank + l.kv_rank + l.rot_dim : w.qd + w.kd + w.vd;
+        w.aw = l.n_heads * a_dv;
+        if (latent) {
+            a->max_rq = std::max(a->max_rq, l.q_rank);
+            a->max_lq = std::max(a->max_lq, l.n_heads * (l.qk_dim + l.rot_dim));
+            a->max_qa = std::max(a->max_qa, w.qd);
+            a->max_att2 = std::max(a->max_att2, w.od);
+            a->max_k = std::max(a->max_k, l.q_rank);
+        }
+        if (l.v_mix) {
+            if (a->vsrc_w && a->vsrc_w != w.vd) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: value rows of %d entries cannot blend with rows of %d", i, w.vd, a->vsrc_w));
+            if (!a->vsrc_w && l.v_mix != PS_VMIX_SOURCE) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d blends its values but no earlier layer supplies any", i));
+            a->vsrc_w = w.vd;
+        }
+        a->max_qkv = std::max(a->max_qkv, w.pw);
+        a->max_od = std::max(a->max_od, w.aw);
         a->max_h = std::max(a->max_h, l.n_heads);
-        a->max_dv = std::max(a->max_dv, l.v_dim);
+        a->max_dv = std::max(a->max_dv, a_dv);
         a->max_k = std::max(a->max_k, std::max(d.dim, w.od));
+        if (l.mlp_kind == PS_MLP_DENSE) {
+            a->max_ff = std::max(a->max_ff, l.expert_ff);
+            a->max_k = std::max(a->max_k, l.expert_ff);
+        }
         if (l.mlp_kind == PS_MLP_ROUTED) {
             a->max_top = std::max(a->max_top, l.top_k);
             a->max_ff = std::max(a->max_ff, l.expert_ff);
@@ -259,6 +309,14 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     a->ldP = (d.n_ctx + PA_DS_KEYS - 1) / PA_DS_KEYS;
     AL(a->pm, 4 * (size_t)a->max_h * a->ldP);
     AL(a->pl, 4 * (size_t)a->max_h * a->ldP);
+    AL(a->x2, 4 * dim);
+    if (a->max_rq) {
+        AL(a->cq, 4 * (size_t)a->max_rq * B);
+        AL(a->lq, 4 * (size_t)a->max_lq * B);
+        AL(a->qa, 4 * (size_t)a->max_qa * B);
+        AL(a->att2, 4 * (size_t)a->max_att2 * B);
+    }
+    if (a->vsrc_w) AL(a->vsrc, 4 * (size_t)a->vsrc_w * B);
     if (rc) return bail(rc);
     int dev = 0;
     cudaGetDevice(&dev);
@@ -297,7 +355,7 @@ size_t ps_arch_v_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(si
 float *ps_arch_logits(PsArch *a) { return a->logits; }
 void ps_arch_set_taps(PsArch *a, int on) { a->taps_on = on; }
 const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 0 && (size_t)layer < a->taps.size()) ? a->taps[(size_t)layer] : nullptr; }
-bool ps_arch_step_replayable(const PsArch *a) { return !a->opt_simple && !a->taps_on; }
+bool ps_arch_step_replayable(const PsArch *a) { return !a->opt_simple && !a->taps_on && !a->has_seq; }
 int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
@@ -325,6 +383,10 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
     if ((rc = aalloc(a, (void **)&a->embed, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->embed, wt->embed, dim * d.vocab_size, "embed", err))) return rc;
     if ((rc = aalloc(a, (void **)&a->head, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->head, wt->head, dim * d.vocab_size, "head", err))) return rc;
     if ((rc = vec(&a->final_norm, wt->final_norm, dim, "final norm", d.norm_unit_offset != 0))) return rc;
+    auto mat = [&](bf16 **dst, const ps_cuda_tensor &t, size_t n, const char *what) -> int {
+        int r = aalloc(a, (void **)dst, 2 * n, err);
+        return r ? r : upload_mat(*dst, t, n, what, err);
+    };
     a->taps.assign((size_t)d.n_layers, nullptr);
     for (int i = 0; i < d.n_layers; i++) {
         PsArchLayer &w = a->L[(size_t)i];
@@ -334,11 +396,56 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         snprintf(nm, sizeof nm, "layer %d", i);
         if ((rc = vec(&w.norm, s.norm, dim, nm, d.norm_unit_offset != 0))) return rc;
         const size_t nq = (size_t)w.qd, nk = (size_t)w.kd, nv = (size_t)w.vd;
-        if ((rc = aalloc(a, (void **)&w.wqkv, 2 * (nq + nk + nv) * dim, err))) return rc;
-        if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
-            (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
+        if ((rc = aalloc(a, (void **)&w.wqkv, 2 * (size_t)w.pw * dim, err))) return rc;
+        if (l.mixer_kind == PS_MIXER_LATENT) {
+            const size_t H = (size_t)l.n_heads, rq = (size_t)l.q_rank, rk = (size_t)l.kv_rank, dr = (size_t)l.rot_dim, dn = (size_t)l.qk_dim, dv = (size_t)l.v_dim;
+            if ((rc = upload_mat(w.wqkv, s.dq, rq * dim, "dq", err)) || (rc = upload_mat(w.wqkv + rq * dim, s.dkv, (rk + dr) * dim, "dkv", err))) return rc;
+            if ((rc = mat(&w.wuq, s.uq, H * (dn + dr) * rq, "uq")) || (rc = mat(&w.wuv, s.uv, H * dv * rk, "uv"))) return rc;
+            if ((rc = vec(&w.dq_norm, s.dq_norm, rq, "dq norm", false)) || (rc = vec(&w.dkv_norm, s.dkv_norm, rk, "dkv norm", false))) return rc;
+            // W_uk [H * dn][rk] -> per head transposed [H][rk][dn]: q_h . (W_uk,h c) = (W_uk,h^T q_h) . c
+            if (!s.uk.host || s.uk.type != PS_TYPE_BF16) return afail(err, PS_CUDA_ERR_INVALID, "bind: matrix uk is missing or not bfloat16");
+            std::vector<uint16_t> tr(H * rk * dn);
+            const uint16_t *src = static_cast<const uint16_t *>(s.uk.host);
+            for (size_t hh = 0; hh < H; hh++)
+                for (size_t r = 0; r < dn; r++)
+                    for (size_t c = 0; c < rk; c++) tr[(hh * rk + c) * dn + r] = src[(hh * dn + r) * rk + c];
+            if ((rc = aalloc(a, (void **)&w.wukt, 2 * tr.size(), err))) return rc;
+            PA_CK(cudaMemcpy(w.wukt, tr.data(), 2 * tr.size(), cudaMemcpyHostToDevice));
+            if (l.rope_dims > 0) {
+                // rotation frequencies, evaluated once on the host in double and rounded to float32
+                const int dims = l.rope_dims, half = dims / 2;
+                std::vector<float> f((size_t)half);
+                double lo = 0, hi = 0;
+                if (l.rope_factor > 0.f) {
+                    auto corr = [&](double turns) { return dims * std::log((double)l.rope_original / (2.0 * M_PI * turns)) / (2.0 * std::log((double)l.rope_base)); };
+                    lo = std::max(std::floor(corr(l.rope_fast)), 0.0);
+                    hi = std::min(std::ceil(corr(l.rope_slow)), (double)(dims - 1));
+                    w.rope_mscale = (float)(0.1 * std::log((double)l.rope_factor) + 1.0);
+                }
+                for (int k = 0; k < half; k++) {
+                    double fr = std::pow((double)l.rope_base, -2.0 * k / dims);
+                    if (l.rope_factor > 0.f) {
+                        const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
+                        fr = fr / l.rope_factor * ramp + fr * (1.0 - ramp);
+                    }
+                    f[(size_t)k] = (float)fr;
+                }
+                if ((rc = upload_f32(a, &w.rope_freq, f, err))) return rc;
+            }
+        } else if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
+                   (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
             return rc;
         if ((rc = aalloc(a, (void **)&w.wo, 2 * dim * (size_t)w.od, err)) || (rc = upload_mat(w.wo, s.o, dim * (size_t)w.od, "o", err))) return rc;
+        if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
+            if (l.post_norm && (rc = vec(&w.norm_mix_out, s.norm_mix_out, dim, "norm of the mixer's output", d.norm_unit_offset != 0))) return rc;
+            if (l.mlp_kind != PS_MLP_NONE) {
+                if ((rc = vec(&w.norm_ff, s.norm_ff, dim, "norm before the feed-forward", d.norm_unit_offset != 0))) return rc;
+                if (l.post_norm && (rc = vec(&w.norm_ff_out, s.norm_ff_out, dim, "norm of the feed-forward's output", d.norm_unit_offset != 0))) return rc;
+            }
+        }
+        if (l.log_bias && ((rc = vec(&w.r1, s.r1, (size_t)l.n_heads, "distance-bias slopes", false)) || (rc = vec(&w.r2, s.r2, (size_t)l.n_heads, "distance-bias rates", false)))) return rc;
+        if (l.sink == PS_SINK_LEARNED && (rc = vec(&w.sink_v, s.sink, (size_t)l.n_heads, "sink logits", false))) return rc;
+        if (l.v_mix == PS_VMIX_BLEND && (rc = vec(&w.vmix, s.vmix, 1, "value blend weight", false))) return rc;
         if (l.proj_bias) {
             std::vector<float> b, part;
             for (auto pr : {std::make_pair(&s.q_bias, nq), std::make_pair(&s.k_bias, nk), std::make_pair(&s.v_bias, nv)}) {
@@ -370,6 +477,11 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                     (rc = upload_mat(w.wdown + e * ff * dim, s.down[e], ff * dim, "expert down", err)))
                     return rc;
         }
+        if (l.mlp_kind == PS_MLP_DENSE) {
+            const size_t ff = (size_t)l.expert_ff;
+            if (!s.gate || !s.up || !s.down) return afail(err, PS_CUDA_ERR_INVALID, "bind: layer %d has no feed-forward tensors", i);
+            if ((rc = mat(&w.wgate, s.gate[0], ff * dim, "gate")) || (rc = mat(&w.wup, s.up[0], ff * dim, "up")) || (rc = mat(&w.wdown, s.down[0], ff * dim, "down"))) return rc;
+        }
     }
     if (a->round) {
         // tensor-core operand blocks: every matrix once more in the layout the tcgen05 GEMM streams (ps_arch_tc.cuh)
@@ -384,7 +496,11 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         if ((rc = tile(&a->t_head, a->head, 1, d.vocab_size, d.dim))) return rc;
         for (int i = 0; i < d.n_layers; i++) {
             PsArchLayer &w = a->L[(size_t)i];
-            if ((rc = tile(&w.t_qkv, w.wqkv, 1, w.qd + w.kd + w.vd, d.dim)) || (rc = tile(&w.t_o, w.wo, 1, d.dim, w.od))) return rc;
+            if ((rc = tile(&w.t_qkv, w.wqkv, 1, w.pw, d.dim)) || (rc = tile(&w.t_o, w.wo, 1, d.dim, w.od))) return rc;
+            if (w.wuq && (rc = tile(&w.t_uq, w.wuq, 1, w.d.n_heads * (w.d.qk_dim + w.d.rot_dim), w.d.q_rank))) return rc;
+            if (w.d.mlp_kind == PS_MLP_DENSE &&
+                ((rc = tile(&w.t_gate, w.wgate, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_down, w.wdown, 1, d.dim, w.d.expert_ff))))
+                return rc;
             if (w.d.mlp_kind == PS_MLP_ROUTED &&
                 ((rc = tile(&w.t_gate, w.wgate, w.d.n_experts, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, w.d.n_experts, w.d.expert_ff, d.dim)) ||
                  (rc = tile(&w.t_down, w.wdown, w.d.n_experts, d.dim, w.d.expert_ff))))
@@ -405,7 +521,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     cudaStream_t st = io.stream;
     const dim3 blk(256);
     auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
-    const bool single = bs == 1 && !a->opt_simple;
+    const bool single = bs == 1 && !a->opt_simple && !a->has_seq;
+    const int groups = std::max(1, d.norm_groups);
     // warps sharing a row pair in the single-token mat-vecs: enough CTAs to fill the GPU when the matrix has few rows
     auto pick_ksplit = [&](int rows, int K) {
         int ks = 1;
@@ -433,11 +550,116 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return 0;
     };
 
+    // y = X W^T for a batch: tensor cores on rounded operands, or the fp32-FMA tiles
+    auto linear = [&](const float *X, int ldx, int K, const bf16 *W, const uint8_t *Wt, int N, float *Cout, int ldc) -> int {
+        if (tc) return tc_dense(X, ldx, bs, K, Wt, N, nullptr, Cout, ldc);
+        pa_k_linear<ROUND><<<dim3(cdiv(N, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(X, ldx, W, nullptr, Cout, ldc, bs, N, K, 0, 0);
+        PA_LAUNCH();
+        return 0;
+    };
+    // per-head products (blockIdx.z = head): fp32-FMA tiles in both modes
+    auto linear_heads = [&](const float *X, int ldx, int x_gs, int K, const bf16 *W, int N, float *Cout, int ldc, int c_gs, int heads) -> int {
+        pa_k_linear<ROUND><<<dim3(cdiv(N, PA_TN), cdiv(bs, PA_TM), (unsigned)heads), blk, 0, st>>>(X, ldx, W, nullptr, Cout, ldc, bs, N, K, x_gs, c_gs);
+        PA_LAUNCH();
+        return 0;
+    };
+    // scores -> soft-max -> P.V of a batch against the cache rows 0 .. n_kv - 1 (keys before the first query's window are skipped)
+    auto attend = [&](const PaAttn &at, const float *q, int ldq, int kd, int li, int aw) -> int {
+        const int tile0 = (at.window > 0 ? std::max(0, pos0 - at.window + 1) : 0) / PA_TN;
+        pa_k_scores<<<dim3(cdiv(n_kv, PA_TN) - tile0, cdiv(bs, PA_TM), at.H), blk, 0, st>>>(at, q, ldq, io.kc[li], kd, a->S, io.pos_dev, bs, tile0);
+        PA_LAUNCH();
+        pa_k_mix_softmax<<<bs, 256, 4 * (size_t)at.H * at.H, st>>>(at, a->S, io.pos_dev, bs);
+        PA_LAUNCH();
+        pa_k_pv<<<dim3(cdiv(at.dv, PA_TN), cdiv(bs, PA_TM), at.H), blk, 0, st>>>(at, a->S, io.vct[li], a->att, aw, io.pos_dev, bs);
+        PA_LAUNCH();
+        return 0;
+    };
+    // sequential blocks: a sublayer's output waits here until the next seam adds it (normed) to the residual stream
+    const float *pend_y = nullptr, *pend_w = nullptr;
+    auto seam = [&](float *h_out, const float *w_in) -> int {
+        pa_k_seam_norm<<<bs, 256, 0, st>>>(a->x, pend_y, pend_w, h_out, w_in, dim, groups, d.norm_eps);
+        PA_LAUNCH();
+        pend_y = pend_w = nullptr;
+        return 0;
+    };
+    auto seq_layer = [&](int li) -> int {
+        const PsArchLayer &w = a->L[(size_t)li];
+        const ps_cuda_layer_desc &l = w.d;
+        const int H = l.n_heads, G = l.n_kv_heads;
+        const bool latent = l.mixer_kind == PS_MIXER_LATENT;
+        int rc;
+        if ((rc = seam(a->h, w.norm))) return rc;
+        if ((rc = linear(a->h, dim, dim, w.wqkv, w.t_qkv, w.pw, a->qkv, w.pw))) return rc;
+        PaAttn at{};
+        at.H = H; at.G = G; at.scale = l.score_scale; at.sink = l.sink != PS_SINK_NONE; at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window;
+        at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
+        const float *q = a->qkv;
+        int ldq = w.pw;
+        if (latent) {
+            const int rq = l.q_rank, rk = l.kv_rank, dr = l.rot_dim, dn = l.qk_dim, lqw = H * (dn + dr);
+            const PaRope rope{w.rope_freq, l.rope_dims, w.rope_mscale};
+            pa_k_latent_post<<<bs, 256, 0, st>>>(a->qkv, w.pw, rq, rk, dr, w.dq_norm, w.dkv_norm, d.norm_eps, rope, a->cq, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            PA_LAUNCH();
+            if ((rc = linear(a->cq, rq, rq, w.wuq, w.t_uq, lqw, a->lq, lqw))) return rc;
+            if ((rc = linear_heads(a->lq, lqw, dn + dr, dn, w.wukt, rk, a->qa, w.qd, rk + dr, H))) return rc; // W_uk folded into the query
+            if (dr > 0) {
+                pa_k_rope_q<<<bs, 256, 0, st>>>(a->lq, a->qa, H, dn, dr, rk, rope, io.pos_dev);
+                PA_LAUNCH();
+            }
+            at.dq = rk + dr; at.dv = rk; q = a->qa; ldq = w.qd;
+        } else {
+            at.dq = l.qk_dim; at.dv = l.v_dim;
+            if (l.qk_norm || l.v_mix)
+                pa_k_qkv_post<<<bs, 256, 0, st>>>(a->qkv, w.pw, H, G, l.qk_dim, l.v_dim, l.qk_norm, d.norm_eps, l.v_mix, w.vmix, a->vsrc, a->vsrc_w, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            else
+                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            PA_LAUNCH();
+        }
+        if ((rc = attend(at, q, ldq, w.kd, li, w.aw))) return rc;
+        const float *ain = a->att;
+        if (latent) { // W_uv on every head's weighted sum of latents
+            if ((rc = linear_heads(a->att, w.aw, l.kv_rank, l.kv_rank, w.wuv, l.v_dim, a->att2, w.od, l.v_dim, H))) return rc;
+            ain = a->att2;
+        }
+        if ((rc = linear(ain, w.od, w.od, w.wo, w.t_o, dim, a->ao, dim))) return rc;
+        pend_y = a->ao; pend_w = l.post_norm ? w.norm_mix_out : nullptr;
+        if (l.mlp_kind == PS_MLP_DENSE) {
+            const int ff = l.expert_ff;
+            if ((rc = seam(a->h, w.norm_ff))) return rc;
+            if (tc) {
+                const int nkb = (dim + PT_KB - 1) / PT_KB, n_ct = (bs + PT_N - 1) / PT_N;
+                pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, a->h, dim, bs, dim, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
+                PA_LAUNCH();
+                PtArgs g{};
+                g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
+                g.C = a->y; g.ldc = ff; g.limit = l.act_limit; g.alpha = l.act_alpha; g.shift = l.up_shift; g.err = io.err_dev;
+                pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+            } else {
+                pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wgate, w.wup, a->y, bs, ff, dim, l.act_limit, l.act_alpha, l.up_shift);
+            }
+            PA_LAUNCH();
+            if ((rc = linear(a->y, ff, ff, w.wdown, w.t_down, dim, a->slot, dim))) return rc;
+            pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
+        }
+        return 0;
+    };
+
     pa_k_embed<<<bs, 128, 0, st>>>(a->x, a->embed, io.tokens_dev, dim, d.embed_scale);
     PA_LAUNCH();
     for (int li = 0; li < d.n_layers; li++) {
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
+        if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
+            int rc = seq_layer(li);
+            if (rc) return rc;
+            if (a->taps_on) {
+                if ((rc = seam(nullptr, nullptr))) return rc; // the tap shows the layer's whole effect
+                if (!a->taps[(size_t)li]) { rc = aalloc(a, (void **)&a->taps[(size_t)li], 4 * (size_t)dim * B, err); if (rc) return rc; }
+                PA_CK(cudaMemcpyAsync(a->taps[(size_t)li], a->x, 4 * (size_t)dim * bs, cudaMemcpyDeviceToDevice, st));
+            }
+            continue;
+        }
+        if (pend_y) { int rc = seam(nullptr, nullptr); if (rc) return rc; }
         const int H = l.n_heads, G = l.n_kv_heads, dq = l.qk_dim, dv = l.v_dim, nqkv = w.qd + w.kd + w.vd;
         const bool routed = l.mlp_kind == PS_MLP_ROUTED;
         if (!single) { // (the single-token kernels norm in their prologues)
@@ -474,16 +696,17 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
             PA_LAUNCH();
         }
-        PaAttn at;
+        PaAttn at{};
+        at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window;
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
-        at.mix = w.mix; at.sink = l.sink; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
+        at.mix = w.mix; at.sink = l.sink != PS_SINK_NONE; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
         if (single) {
             pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
             PA_LAUNCH();
             pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();
         } else {
-            pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs);
+            pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs, 0);
             PA_LAUNCH();
             pa_k_mix_softmax<<<bs, 256, 4 * (size_t)H * H, st>>>(at, a->S, io.pos_dev, bs);
             PA_LAUNCH();
@@ -562,8 +785,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     }
     if (lm_head) {
         if (!single) {
-            pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, a->final_norm, dim, d.norm_eps);
-            PA_LAUNCH();
+            if (pend_y || groups > 1) {
+                int rc = seam(a->h, a->final_norm);
+                if (rc) return rc;
+            } else {
+                pa_k_norm<<<bs, 256, 0, st>>>(a->h, a->x, a->final_norm, dim, d.norm_eps);
+                PA_LAUNCH();
+            }
         }
         if (single) {
             PaMv mv{};

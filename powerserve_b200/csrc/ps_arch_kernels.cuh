@@ -20,7 +20,10 @@ struct PaAttn {
     const uint16_t *bucket; // distance -> row, n_bucket entries
     int n_bucket;
     const float *mix;       // [H][H] or null
-    int sink;
+    int sink;               // the denominator has one more term ...
+    const float *sink_v;    // ... exp(sink_v[h]) (null: exp(0))
+    const float *r1, *r2;   // [H] each or null: score -= r1[h] * ln(1 + r2[h] * distance)
+    int window;             // > 0: a query sees the keys at distances 0 .. window - 1 only
     int n_ctx;
     int64_t ldS;            // row stride of the score rows
     int B;                  // rows per head in the score buffer (max_batch)
@@ -134,14 +137,145 @@ __global__ void __launch_bounds__(256) pa_k_combine(float *__restrict__ x, const
     x[(int64_t)t * dim + c] += y;
 }
 
+// ---------------------------------------------------------------------------------------------------------------- sequential blocks
+// block-wide sum over 256 threads, broadcast to all (two barriers)
+__device__ __forceinline__ float pa_block_sum(float s, float *red) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads(); // red may still be read from the call before
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
+    return t;
+}
+
+// The seam between two sublayers of a sequential block, one CTA per token:
+//   y given:  x <- x + G(y; w_out)   (w_out null: x <- x + y)      the sublayer's output, normed, joins the residual stream
+//   h given:  h  = G(x; w_in)                                       the next sublayer's input
+// G cuts the vector into `groups` equal parts and divides each by its own sqrt(mean(part^2) + eps) before the weight.
+__global__ void __launch_bounds__(256) pa_k_seam_norm(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w_out, float *__restrict__ h,
+                                                      const float *__restrict__ w_in, int dim, int groups, float eps) {
+    __shared__ float red[8];
+    const int64_t base = (int64_t)blockIdx.x * dim;
+    const int gs = dim / groups;
+    for (int g = 0; g < groups; g++) {
+        const int c0 = g * gs;
+        if (y) {
+            float inv = 1.0f;
+            if (w_out) {
+                float s = 0.f;
+                for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(y[base + c0 + c], y[base + c0 + c], s);
+                inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
+            }
+            for (int c = threadIdx.x; c < gs; c += 256) x[base + c0 + c] += w_out ? y[base + c0 + c] * inv * w_out[c0 + c] : y[base + c0 + c];
+        }
+        if (h) {
+            float s = 0.f;
+            for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(x[base + c0 + c], x[base + c0 + c], s); // (a thread reads back its own writes)
+            const float inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
+            for (int c = threadIdx.x; c < gs; c += 256) h[base + c0 + c] = x[base + c0 + c] * inv * w_in[c0 + c];
+        }
+    }
+}
+
+// warp-wide: 1 / sqrt(mean(v[0 .. n)^2) + eps)
+__device__ __forceinline__ float pa_warp_inv_rms(const float *v, int n, float eps, int lane) {
+    float s = 0.f;
+    for (int c = lane; c < n; c += 32) s = fmaf(v[c], v[c], s);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return 1.0f / sqrtf(s / (float)n + eps);
+}
+
+// After the q|k|v projection of a batch, one CTA per token: unit-RMS q heads (in place) and k heads (qk_norm), the value rows
+// blended with the source layer's (v_mix), K row -> kc[pos][:], V row transposed -> vct[:][pos].
+__global__ void __launch_bounds__(256) pa_k_qkv_post(float *__restrict__ qkv, int ld, int H, int G, int dq, int dv, int qk_norm, float eps, int v_mix,
+                                                     const float *__restrict__ lambda, float *__restrict__ v_src, int ld_src, float *__restrict__ kc,
+                                                     float *__restrict__ vct, int n_ctx, const int32_t *__restrict__ pos) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, p = pos[t];
+    float *row = qkv + (int64_t)t * ld;
+    const int qd = H * dq, kd = G * dq, vd = G * dv;
+    for (int hh = warp; hh < H + G; hh += 8) { // q heads, then k heads
+        float *v = row + hh * dq;
+        const float inv = qk_norm ? pa_warp_inv_rms(v, dq, eps, lane) : 1.0f;
+        if (hh < H) {
+            if (qk_norm) for (int c = lane; c < dq; c += 32) v[c] *= inv;
+        } else {
+            float *dst = kc + (int64_t)p * kd + (hh - H) * dq;
+            for (int c = lane; c < dq; c += 32) dst[c] = v[c] * inv;
+        }
+    }
+    const float lam = v_mix == PS_VMIX_BLEND ? lambda[0] : 0.f;
+    for (int c = threadIdx.x; c < vd; c += 256) {
+        float v = row[qd + kd + c];
+        if (v_mix == PS_VMIX_SOURCE) v_src[(int64_t)t * ld_src + c] = v;
+        else if (v_mix == PS_VMIX_BLEND) v = (1.0f - lam) * v + lam * v_src[(int64_t)t * ld_src + c];
+        vct[(int64_t)c * n_ctx + p] = v;
+    }
+}
+
+// rotation of the first `dims` entries of a vector (pairs (i, i + dims / 2)) by the angles pos * freq[i], cos / sin times mscale
+struct PaRope {
+    const float *freq; // [dims / 2]
+    int dims;
+    float mscale;
+};
+__device__ __forceinline__ void pa_rope_store(const PaRope &r, const float *src, float *dst, int n, int pos, int c) {
+    const int half = r.dims >> 1;
+    if (c >= r.dims) { if (c < n) dst[c] = src[c]; return; }
+    const int i = c < half ? c : c - half;
+    const float ang = (float)pos * r.freq[i];
+    const float cs = cosf(ang) * r.mscale, sn = sinf(ang) * r.mscale;
+    dst[c] = c < half ? src[c] * cs - src[c + half] * sn : src[c] * cs + src[c - half] * sn;
+}
+
+// After the down-projections W_dq | W_dkv of a latent attention, one CTA per token.  Row t = [q latent (rq) | kv latent (rk) |
+// rotated key part (dr)]: cq = N(q latent; wq) -> cq[t];  c = N(kv latent; wk) -> kc[pos][0 .. rk) and vct[.][pos];
+// rot(key part, pos) -> kc[pos][rk .. rk + dr).
+__global__ void __launch_bounds__(256) pa_k_latent_post(const float *__restrict__ t_in, int ld, int rq, int rk, int dr, const float *__restrict__ wq, const float *__restrict__ wk,
+                                                        float eps, PaRope rope, float *__restrict__ cq, float *__restrict__ kc, float *__restrict__ vct, int n_ctx,
+                                                        const int32_t *__restrict__ pos) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, p = pos[t];
+    const float *row = t_in + (int64_t)t * ld;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < rq; c += 256) s = fmaf(row[c], row[c], s);
+    const float iq = 1.0f / sqrtf(pa_block_sum(s, red) / (float)rq + eps);
+    for (int c = threadIdx.x; c < rq; c += 256) cq[(int64_t)t * rq + c] = row[c] * iq * wq[c];
+    s = 0.f;
+    for (int c = threadIdx.x; c < rk; c += 256) s = fmaf(row[rq + c], row[rq + c], s);
+    const float ik = 1.0f / sqrtf(pa_block_sum(s, red) / (float)rk + eps);
+    float *krow = kc + (int64_t)p * (rk + dr);
+    for (int c = threadIdx.x; c < rk; c += 256) {
+        const float v = row[rq + c] * ik * wk[c];
+        krow[c] = v;
+        vct[(int64_t)c * n_ctx + p] = v;
+    }
+    for (int c = threadIdx.x; c < dr; c += 256) pa_rope_store(rope, row + rq + rk, krow + rk, dr, p, c);
+}
+
+// the rotated part of every query head: q[t][h * (dn + dr) + dn ..] -> qa[t][h * (rk + dr) + rk ..], rotated by the token's position
+__global__ void __launch_bounds__(256) pa_k_rope_q(const float *__restrict__ q, float *__restrict__ qa, int H, int dn, int dr, int rk, PaRope rope, const int32_t *__restrict__ pos) {
+    const int t = blockIdx.x, p = pos[t];
+    for (int e = threadIdx.x; e < H * dr; e += 256) {
+        const int hh = e / dr, c = e % dr;
+        pa_rope_store(rope, q + ((int64_t)t * H + hh) * (dn + dr) + dn, qa + ((int64_t)t * H + hh) * (rk + dr) + rk, dr, p, c);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------- dense
-// C[m][n] = sum_k A[m][k] W[n][k] + bias[n]
+// C[m][n] = sum_k A[m][k] W[n][k] + bias[n].  blockIdx.z walks groups (per-head products): group z reads the columns of A from
+// z * a_gs on, the matrix z of N x K weights, and writes the columns of C from z * c_gs on.
 template <bool ROUND>
 __global__ void __launch_bounds__(256) pa_k_linear(const float *__restrict__ A, int lda, const bf16 *__restrict__ W, const float *__restrict__ bias, float *__restrict__ C, int ldc,
-                                                   int M, int N, int K) {
+                                                   int M, int N, int K, int a_gs = 0, int c_gs = 0) {
     PA_TILE_SMEM(1);
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    A += (int64_t)blockIdx.z * a_gs;
+    C += (int64_t)blockIdx.z * c_gs;
+    W += (int64_t)blockIdx.z * N * K;
     float acc[1][4][4] = {};
     const float *arow = (m0 + lr < M) ? A + (int64_t)(m0 + lr) * lda : nullptr;
     const bf16 *brow = (n0 + lr < N) ? W + (int64_t)(n0 + lr) * K : nullptr;
@@ -282,22 +416,49 @@ __global__ void __launch_bounds__(256) pa_k_expert_down(const float *__restrict_
     }
 }
 
+// dense gated feed-forward, first half: y[m][n] = act(gate[n] . h_m, up[n] . h_m)
+template <bool ROUND>
+__global__ void __launch_bounds__(256) pa_k_dense_up(const float *__restrict__ h, int ldh, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int M, int ff,
+                                                     int dim, float limit, float alpha, float shift) {
+    PA_TILE_SMEM(2);
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    float acc[2][4][4] = {};
+    const float *arow = (m0 + lr < M) ? h + (int64_t)(m0 + lr) * ldh : nullptr;
+    const bool nin = n0 + lr < ff;
+    pa_tile_mm<ROUND, bf16, 2>(acc, arow, 1.0f, nin ? Wg + (int64_t)(n0 + lr) * dim : nullptr, nin ? Wu + (int64_t)(n0 + lr) * dim : nullptr, dim, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < ff) y[(int64_t)m * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], limit, alpha, shift);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------- attention
 __device__ __forceinline__ float pa_score(const PaAttn &at, float dot, int h, int dist) {
     float s = dot * at.scale;
     if (at.temp) s *= at.temp[h];
     if (at.rel) s += at.rel[(int)at.bucket[min(dist, at.n_bucket - 1)] * at.H + h];
+    if (at.r1) s -= at.r1[h] * logf(1.0f + at.r2[h] * (float)dist);
     return s;
 }
+// first key a query at position p sees
+__device__ __forceinline__ int pa_first_key(const PaAttn &at, int p) { return at.window > 0 ? max(0, p - at.window + 1) : 0; }
+__device__ __forceinline__ float pa_sink_logit(const PaAttn &at, int h) { return at.sink_v ? at.sink_v[h] : 0.f; }
 
 // S[h][i][j] = score of query i (position pos[i]) and cache row j <= pos[i], before the heads are mixed
 __global__ void __launch_bounds__(256) pa_k_scores(PaAttn at, const float *__restrict__ qkv, int ldq, const float *__restrict__ kc, int kd, float *__restrict__ S,
-                                                   const int32_t *__restrict__ pos, int bs) {
+                                                   const int32_t *__restrict__ pos, int bs, int key_tile0) {
     PA_TILE_SMEM(1);
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
-    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = (blockIdx.x + key_tile0) * PA_TN;
     const int pos0 = pos[0], last = pos0 + min(m0 + PA_TM, bs) - 1; // the tile's furthest query
-    if (n0 > last) return;
+    if (n0 > last || n0 + PA_TN <= pa_first_key(at, pos0 + m0)) return; // (the tile's first query sees furthest back)
     float acc[1][4][4] = {};
     const float *arow = (m0 + lr < bs) ? qkv + (int64_t)(m0 + lr) * ldq + h * at.dq : nullptr;
     const float *brow = (n0 + lr <= last) ? kc + (int64_t)(n0 + lr) * kd + g * at.dq : nullptr;
@@ -311,7 +472,7 @@ __global__ void __launch_bounds__(256) pa_k_scores(PaAttn at, const float *__res
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n <= p) row[n] = pa_score(at, acc[0][i][j], h, p - n);
+            if (n <= p && n >= pa_first_key(at, p)) row[n] = pa_score(at, acc[0][i][j], h, p - n);
         }
     }
 }
@@ -319,9 +480,9 @@ __global__ void __launch_bounds__(256) pa_k_scores(PaAttn at, const float *__res
 // per query: mix the heads' scores (b_h = sum_g T[h][g] a_g), soft-max every head's row (optionally with a sink term in the
 // denominator), zero the row's tail up to the end of the batch so that P.V can run whole tiles
 template <int MAXH>
-__device__ __forceinline__ void pa_mix_rows(const PaAttn &at, float *S, int i, int n, const float *Ts) {
+__device__ __forceinline__ void pa_mix_rows(const PaAttn &at, float *S, int i, int lo, int n, const float *Ts) {
     const int H = at.H;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    for (int j = lo + threadIdx.x; j < n; j += blockDim.x) {
         float a[MAXH];
 #pragma unroll
         for (int g = 0; g < MAXH; g++) a[g] = g < H ? S[((int64_t)g * at.B + i) * at.ldS + j] : 0.f;
@@ -338,34 +499,37 @@ __device__ __forceinline__ void pa_mix_rows(const PaAttn &at, float *S, int i, i
 __global__ void __launch_bounds__(256) pa_k_mix_softmax(PaAttn at, float *__restrict__ S, const int32_t *__restrict__ pos, int bs) {
     extern __shared__ float Ts[];
     const int i = blockIdx.x, H = at.H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n = pos[i] + 1, n_end = pos[0] + bs;
+    const int n = pos[i] + 1, n_end = pos[0] + bs, lo = pa_first_key(at, pos[i]);
+    const int lo_tile = pa_first_key(at, pos[0] + i / PA_TM * PA_TM); // P.V walks whole tiles of queries: from the tile's first key on
     if (at.mix) {
         for (int t = threadIdx.x; t < H * H; t += 256) Ts[t] = at.mix[t];
         __syncthreads();
-        if (H <= 8) pa_mix_rows<8>(at, S, i, n, Ts);
-        else if (H <= 16) pa_mix_rows<16>(at, S, i, n, Ts);
-        else if (H <= 32) pa_mix_rows<32>(at, S, i, n, Ts);
-        else pa_mix_rows<PA_MAX_HEADS>(at, S, i, n, Ts);
+        if (H <= 8) pa_mix_rows<8>(at, S, i, lo, n, Ts);
+        else if (H <= 16) pa_mix_rows<16>(at, S, i, lo, n, Ts);
+        else if (H <= 32) pa_mix_rows<32>(at, S, i, lo, n, Ts);
+        else pa_mix_rows<PA_MAX_HEADS>(at, S, i, lo, n, Ts);
         __syncthreads();
     }
     for (int h = warp; h < H; h += 8) {
         float *row = S + ((int64_t)h * at.B + i) * at.ldS;
-        float mx = at.sink ? 0.f : -INFINITY;
-        for (int j = lane; j < n; j += 32) mx = fmaxf(mx, row[j]);
+        const float sk = pa_sink_logit(at, h);
+        float mx = at.sink ? sk : -INFINITY;
+        for (int j = lo + lane; j < n; j += 32) mx = fmaxf(mx, row[j]);
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.f;
-        for (int j = lane; j < n; j += 32) {
+        for (int j = lo + lane; j < n; j += 32) {
             const float e = expf(row[j] - mx);
             row[j] = e;
             sum += e;
         }
 #pragma unroll
         for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (at.sink) sum += expf(-mx);
+        if (at.sink) sum += expf(sk - mx);
         const float inv = 1.0f / sum;
-        for (int j = lane; j < n; j += 32) row[j] *= inv;
+        for (int j = lo + lane; j < n; j += 32) row[j] *= inv;
         for (int j = n + lane; j < n_end; j += 32) row[j] = 0.f;
+        for (int j = lo_tile + lane; j < lo; j += 32) row[j] = 0.f;
     }
 }
 
@@ -376,10 +540,11 @@ __global__ void __launch_bounds__(256) pa_k_pv(PaAttn at, const float *__restric
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
     const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
     const int n_keys = pos[0] + min(m0 + PA_TM, bs); // keys the tile's furthest query sees (the rows are zero beyond their own)
+    const int k0 = pa_first_key(at, pos[0] + m0);    // ... and the first key its first query sees (zero before a row's own)
     float acc[1][4][4] = {};
-    const float *arow = (m0 + lr < bs) ? S + ((int64_t)h * at.B + m0 + lr) * at.ldS : nullptr;
-    const float *brow = (n0 + lr < at.dv) ? vct + (int64_t)(g * at.dv + n0 + lr) * at.n_ctx : nullptr;
-    pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, n_keys, As, Bs);
+    const float *arow = (m0 + lr < bs) ? S + ((int64_t)h * at.B + m0 + lr) * at.ldS + k0 : nullptr;
+    const float *brow = (n0 + lr < at.dv) ? vct + (int64_t)(g * at.dv + n0 + lr) * at.n_ctx + k0 : nullptr;
+    pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, n_keys - k0, As, Bs);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;
