@@ -74,3 +74,72 @@ def write_model_dir(path: str, cfg: dict, tensors: Dict[str, np.ndarray]) -> str
         json.dump(cfg, f, indent=1)
     safetensors.write_file(os.path.join(path, "model.safetensors"), tensors)
     return path
+
+
+# ------------------------------------------------------------------------------------------------------------ Vanapel
+def vanapel_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, *, window: int, scale: Optional[float] = None, v_mix: bool = False,
+                            ff: int = 0, limit: float = 1.0) -> dict:
+    """a windowed-attention entry of a Vanapel layer list; ff == 0 means a layer without a feed-forward"""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "scale": float(scale if scale is not None else dim ** -0.5)}
+    if v_mix:
+        mixer["v_mix"] = True
+    return {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff, "limit": limit} if ff else None}
+
+
+def vanapel_latent_layer(heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, *, scale: Optional[float] = None, rope_base: float = 10000.0,
+                         rope_dims: Optional[int] = None, scaling: Optional[dict] = None, ff: int = 0, limit: float = 1.0) -> dict:
+    """a latent-attention entry; `scaling` = {"factor", "original", "fast", "slow"} turns YaRN on"""
+    rot = {"base": rope_base, "dims": rot_dim if rope_dims is None else rope_dims}
+    if scaling:
+        rot["scaling"] = dict(scaling)
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "rot": rot,
+             "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5)}
+    return {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff, "limit": limit} if ff else None}
+
+
+def vanapel_config(width: int, vocab: int, layers: List[dict], *, eps: float = 1e-6, groups: int = 1) -> dict:
+    return {"architecture": "Vanapel", "layers": layers, "norm": {"eps": eps, "groups": groups}, "vocab": vocab, "width": width}
+
+
+def vanapel_weights(cfg: dict, seed: int = 0, fast: bool = False) -> Dict[str, np.ndarray]:
+    """float32 arrays of bfloat16-representable values keyed by tensor name (fast = True: big matrices as random bfloat16 bit patterns)"""
+    rng = np.random.default_rng(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(a):
+        return (safetensors.float32_to_bf16_bits(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)
+
+    def mat(out_dim, in_dim, gain=1.0):
+        if fast:
+            e = int(np.floor(np.log2(gain / np.sqrt(in_dim)))) + 127
+            bits = rng.integers(0, 1 << 7, size=(out_dim, in_dim), dtype=np.uint16) | np.uint16(e << 7)
+            return bits | (rng.integers(0, 2, size=(out_dim, in_dim), dtype=np.uint16) << 15).astype(np.uint16)
+        return rnd(rng.standard_normal((out_dim, in_dim), dtype=np.float32) * np.float32(gain / np.sqrt(in_dim)))
+
+    def norm_w(n, mean=1.0):
+        return rnd(mean + rng.standard_normal(n).astype(np.float32) * 0.1)
+
+    t: Dict[str, np.ndarray] = {"embed": mat(V, W, np.sqrt(W)), "final.norm": norm_w(W), "head": mat(V, W)}
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        H, dv = m["heads"], m["vdim"]
+        t[p + "norm1"], t[p + "norm1b"] = norm_w(W), norm_w(W, 0.5)
+        if l["type"] == "attention":
+            G, dq = m["kv_heads"], m["dim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * dq, W), mat(G * dq, W), mat(G * dv, W)
+            t[p + "mix.r1"] = rnd(rng.uniform(0.05, 0.6, H))
+            t[p + "mix.r2"] = rnd(rng.uniform(0.05, 1.5, H))
+            if m.get("v_mix"):
+                t[p + "mix.vmix"] = rnd(np.array(rng.uniform(0.2, 0.8), np.float32))
+        else:
+            dn, dr, rq, rk = m["dim"], m["rot_dim"], m["q_rank"], m["kv_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"], t[p + "mix.uq"] = mat(rq, W), norm_w(rq), mat(H * (dn + dr), rq, 2.0)
+            t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(rk + dr, W, 2.0), norm_w(rk)
+            t[p + "mix.uk"], t[p + "mix.uv"] = mat(H * dn, rk, 2.0), mat(H * dv, rk)
+        t[p + "mix.sink"] = rnd(rng.standard_normal(H).astype(np.float32))
+        t[p + "mix.o"] = mat(W, H * dv)
+        if l.get("mlp") is not None:
+            ff = l["mlp"]["ff"]
+            t[p + "norm2"], t[p + "norm2b"] = norm_w(W), norm_w(W, 0.5)
+            t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = mat(ff, W, 1.5), mat(ff, W, 1.5), mat(W, ff)
+    return t

@@ -160,6 +160,7 @@ def load_library() -> C.CDLL:
         "ps_cuda_host_expf_ref": (C.c_float, [C.c_float]),
         "ps_cuda_host_v_expf": (C.c_float, [C.c_float]),
         "ps_cuda_host_rel_bucket": (ci, [ci, ci, C.c_float]),
+        "ps_cuda_host_rope_freq": (C.c_float, [ci, C.c_float, C.c_float, ci, C.c_float, C.c_float, C.POINTER(C.c_float)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)   # AttributeError here == the library does not export what include/ps_cuda.h declares

@@ -79,7 +79,7 @@ struct PsArch {
     int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, four for long streams or without overlap)
     int opt_prefetch = 1; // 1: a mat-vec CTA requests its first row group into L2 before the dependency wait; 2: every next group too
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
-    bool has_seq = false; // some layer is a sequential block
+    bool has_seq = false, has_par = false; // some layer is a sequential / a parallel block
 };
 
 namespace {
@@ -205,6 +205,28 @@ extern "C" int ps_cuda_host_rel_bucket(int distance, int rows, float max_dist) {
     return (int)t[(size_t)distance];
 }
 
+// rotation frequencies of `dims` rotated dims, evaluated once on the host in double and rounded to float32: base^(-2 i / dims),
+// with factor > 0 blended towards f_i / factor along YaRN's ramp; returns the factor on cos / sin
+extern "C" float ps_cuda_host_rope_freq(int dims, float base, float factor, int original, float fast, float slow, float *freq) {
+    const int half = dims / 2;
+    double lo = 0, hi = 0, mscale = 1.0;
+    if (factor > 0.f) {
+        auto corr = [&](double turns) { return dims * std::log((double)original / (2.0 * M_PI * turns)) / (2.0 * std::log((double)base)); };
+        lo = std::max(std::floor(corr(fast)), 0.0);
+        hi = std::min(std::ceil(corr(slow)), (double)(dims - 1));
+        mscale = 0.1 * std::log((double)factor) + 1.0;
+    }
+    for (int k = 0; k < half; k++) {
+        double fr = std::pow((double)base, -2.0 * k / dims);
+        if (factor > 0.f) {
+            const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
+            fr = fr / factor * ramp + fr * (1.0 - ramp);
+        }
+        freq[k] = (float)fr;
+    }
+    return (float)mscale;
+}
+
 int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err) {
     *out = nullptr;
     const ps_cuda_arch_desc &d = *desc;
@@ -221,7 +243,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         const ps_cuda_layer_desc &l = d.layers[i];
         PsArchLayer &w = a->L[(size_t)i];
         w.d = l;
-        if (l.block_kind == PS_BLOCK_SEQUENTIAL) a->has_seq = true;
+        (l.block_kind == PS_BLOCK_SEQUENTIAL ? a->has_seq : a->has_par) = true;
         if (l.mixer_kind != PS_MIXER_ATTENTION && l.mixer_kind != PS_MIXER_LATENT) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
         const bool latent = l.mixer_kind == PS_MIXER_LATENT;
         if (latent && (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) ||
@@ -327,6 +349,8 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         cudaFuncSetAttribute(pa_k_dec_mv<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_expert_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_expert_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_dense_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_dec_dense_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
@@ -355,7 +379,7 @@ size_t ps_arch_v_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(si
 float *ps_arch_logits(PsArch *a) { return a->logits; }
 void ps_arch_set_taps(PsArch *a, int on) { a->taps_on = on; }
 const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 0 && (size_t)layer < a->taps.size()) ? a->taps[(size_t)layer] : nullptr; }
-bool ps_arch_step_replayable(const PsArch *a) { return !a->opt_simple && !a->taps_on && !a->has_seq; }
+bool ps_arch_step_replayable(const PsArch *a) { return !a->opt_simple && !a->taps_on && !(a->has_seq && a->has_par); }
 int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_simple")) { a->opt_simple = value; return 1; }
     if (!strcmp(name, "arch_taps")) { a->taps_on = value; return 1; }
@@ -412,24 +436,8 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
             if ((rc = aalloc(a, (void **)&w.wukt, 2 * tr.size(), err))) return rc;
             PA_CK(cudaMemcpy(w.wukt, tr.data(), 2 * tr.size(), cudaMemcpyHostToDevice));
             if (l.rope_dims > 0) {
-                // rotation frequencies, evaluated once on the host in double and rounded to float32
-                const int dims = l.rope_dims, half = dims / 2;
-                std::vector<float> f((size_t)half);
-                double lo = 0, hi = 0;
-                if (l.rope_factor > 0.f) {
-                    auto corr = [&](double turns) { return dims * std::log((double)l.rope_original / (2.0 * M_PI * turns)) / (2.0 * std::log((double)l.rope_base)); };
-                    lo = std::max(std::floor(corr(l.rope_fast)), 0.0);
-                    hi = std::min(std::ceil(corr(l.rope_slow)), (double)(dims - 1));
-                    w.rope_mscale = (float)(0.1 * std::log((double)l.rope_factor) + 1.0);
-                }
-                for (int k = 0; k < half; k++) {
-                    double fr = std::pow((double)l.rope_base, -2.0 * k / dims);
-                    if (l.rope_factor > 0.f) {
-                        const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
-                        fr = fr / l.rope_factor * ramp + fr * (1.0 - ramp);
-                    }
-                    f[(size_t)k] = (float)fr;
-                }
+                std::vector<float> f((size_t)l.rope_dims / 2);
+                w.rope_mscale = ps_cuda_host_rope_freq(l.rope_dims, l.rope_base, l.rope_factor, l.rope_original, l.rope_fast, l.rope_slow, f.data());
                 if ((rc = upload_f32(a, &w.rope_freq, f, err))) return rc;
             }
         } else if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
@@ -521,7 +529,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     cudaStream_t st = io.stream;
     const dim3 blk(256);
     auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
-    const bool single = bs == 1 && !a->opt_simple && !a->has_seq;
+    // single tokens take the single-token kernels; a model that mixes both block kinds, and taps of sequential blocks, take the batch kernels
+    const bool single = bs == 1 && !a->opt_simple && !(a->has_seq && (a->has_par || a->taps_on));
     const int groups = std::max(1, d.norm_groups);
     // warps sharing a row pair in the single-token mat-vecs: enough CTAs to fill the GPU when the matrix has few rows
     auto pick_ksplit = [&](int rows, int K) {
@@ -582,14 +591,46 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         pend_y = pend_w = nullptr;
         return 0;
     };
+    // the single-token step of sequential blocks: the residual stream alternates between two buffers, because the CTA that stores the
+    // seam's sum must not overwrite what the other CTAs of the same launch still read
+    float *xc = a->x, *xo = a->x2;
+    auto seam_mv = [&](PaMv &mv, const float *norm_w) {
+        mv.x = xc; mv.groups = groups; mv.eps = d.norm_eps; mv.norm_w = norm_w; mv.seam_y = pend_y; mv.seam_w = pend_w;
+        if (pend_y) { mv.x_out = xo; std::swap(xc, xo); }
+        pend_y = pend_w = nullptr;
+    };
+    auto dec_mv = [&](PaMv &mv, size_t smem) -> int {
+        mv.ksplit = pick_ksplit(mv.N, mv.K); mv.prefetch = a->opt_prefetch;
+        pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(mv.N, mv.ksplit, mv.K)), dim3(PA_DV_THREADS), smem, st, mv);
+        PA_LAUNCH();
+        return 0;
+    };
+    // scores and P.V of one query against the cache; the grids do not depend on the position (a window bounds the blocks of keys)
+    auto attend_single = [&](const PaAttn &at, const float *q, int li) -> int {
+        unsigned blocks = cdiv(n_kv_cap, PA_DS_KEYS);
+        if (at.window > 0) blocks = std::min(blocks, cdiv(at.window, PA_DS_KEYS) + 1);
+        pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
+        PA_LAUNCH();
+        pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
+                      pa_dec_pv_chunk(at.H, at.G), io.err_dev);
+        PA_LAUNCH();
+        return 0;
+    };
     auto seq_layer = [&](int li) -> int {
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
         const int H = l.n_heads, G = l.n_kv_heads;
         const bool latent = l.mixer_kind == PS_MIXER_LATENT;
         int rc;
-        if ((rc = seam(a->h, w.norm))) return rc;
-        if ((rc = linear(a->h, dim, dim, w.wqkv, w.t_qkv, w.pw, a->qkv, w.pw))) return rc;
+        if (single) {
+            PaMv mv{};
+            seam_mv(mv, w.norm);
+            mv.W = w.wqkv; mv.N = w.pw; mv.K = dim; mv.y = a->qkv;
+            if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
+        } else {
+            if ((rc = seam(a->h, w.norm))) return rc;
+            if ((rc = linear(a->h, dim, dim, w.wqkv, w.t_qkv, w.pw, a->qkv, w.pw))) return rc;
+        }
         PaAttn at{};
         at.H = H; at.G = G; at.scale = l.score_scale; at.sink = l.sink != PS_SINK_NONE; at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window;
         at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
@@ -600,8 +641,17 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             const PaRope rope{w.rope_freq, l.rope_dims, w.rope_mscale};
             pa_k_latent_post<<<bs, 256, 0, st>>>(a->qkv, w.pw, rq, rk, dr, w.dq_norm, w.dkv_norm, d.norm_eps, rope, a->cq, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
             PA_LAUNCH();
-            if ((rc = linear(a->cq, rq, rq, w.wuq, w.t_uq, lqw, a->lq, lqw))) return rc;
-            if ((rc = linear_heads(a->lq, lqw, dn + dr, dn, w.wukt, rk, a->qa, w.qd, rk + dr, H))) return rc; // W_uk folded into the query
+            if (single) {
+                PaMv mv{};
+                mv.x = a->cq; mv.W = w.wuq; mv.N = lqw; mv.K = rq; mv.y = a->lq;
+                if ((rc = dec_mv(mv, 0))) return rc;
+                PaMv mk{}; // W_uk folded into the query, head by head
+                mk.x = a->lq; mk.W = w.wukt; mk.N = H * rk; mk.K = dn; mk.y = a->qa; mk.grp_rows = rk; mk.x_gs = dn + dr; mk.y_gs = rk + dr;
+                if ((rc = dec_mv(mk, 0))) return rc;
+            } else {
+                if ((rc = linear(a->cq, rq, rq, w.wuq, w.t_uq, lqw, a->lq, lqw))) return rc;
+                if ((rc = linear_heads(a->lq, lqw, dn + dr, dn, w.wukt, rk, a->qa, w.qd, rk + dr, H))) return rc; // W_uk folded into the query
+            }
             if (dr > 0) {
                 pa_k_rope_q<<<bs, 256, 0, st>>>(a->lq, a->qa, H, dn, dr, rk, rope, io.pos_dev);
                 PA_LAUNCH();
@@ -615,15 +665,42 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
             PA_LAUNCH();
         }
-        if ((rc = attend(at, q, ldq, w.kd, li, w.aw))) return rc;
+        if (single) {
+            if ((rc = attend_single(at, q, li))) return rc;
+        } else if ((rc = attend(at, q, ldq, w.kd, li, w.aw))) {
+            return rc;
+        }
         const float *ain = a->att;
         if (latent) { // W_uv on every head's weighted sum of latents
-            if ((rc = linear_heads(a->att, w.aw, l.kv_rank, l.kv_rank, w.wuv, l.v_dim, a->att2, w.od, l.v_dim, H))) return rc;
+            if (single) {
+                PaMv mv{};
+                mv.x = a->att; mv.W = w.wuv; mv.N = w.od; mv.K = l.kv_rank; mv.y = a->att2; mv.grp_rows = l.v_dim; mv.x_gs = l.kv_rank; mv.y_gs = l.v_dim;
+                if ((rc = dec_mv(mv, 0))) return rc;
+            } else if ((rc = linear_heads(a->att, w.aw, l.kv_rank, l.kv_rank, w.wuv, l.v_dim, a->att2, w.od, l.v_dim, H))) {
+                return rc;
+            }
             ain = a->att2;
         }
-        if ((rc = linear(ain, w.od, w.od, w.wo, w.t_o, dim, a->ao, dim))) return rc;
+        if (single) {
+            PaMv mv{};
+            mv.x = ain; mv.W = w.wo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
+            if ((rc = dec_mv(mv, 0))) return rc;
+        } else if ((rc = linear(ain, w.od, w.od, w.wo, w.t_o, dim, a->ao, dim))) {
+            return rc;
+        }
         pend_y = a->ao; pend_w = l.post_norm ? w.norm_mix_out : nullptr;
-        if (l.mlp_kind == PS_MLP_DENSE) {
+        if (l.mlp_kind == PS_MLP_DENSE && single) {
+            const int ff = l.expert_ff;
+            float *xout = xo;
+            pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)(4 * a->n_sm))), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc,
+                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, l.act_limit, l.act_alpha, l.up_shift);
+            PA_LAUNCH();
+            std::swap(xc, xo);
+            PaMv mv{};
+            mv.x = a->y; mv.W = w.wdown; mv.N = dim; mv.K = ff; mv.y = a->slot;
+            if ((rc = dec_mv(mv, 0))) return rc;
+            pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
+        } else if (l.mlp_kind == PS_MLP_DENSE) {
             const int ff = l.expert_ff;
             if ((rc = seam(a->h, w.norm_ff))) return rc;
             if (tc) {
@@ -796,6 +873,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         if (single) {
             PaMv mv{};
             mv.x = a->x; mv.norm_w = a->final_norm; mv.eps = d.norm_eps; mv.W = a->head; mv.N = d.vocab_size; mv.K = dim; mv.y = a->logits;
+            if (a->has_seq) seam_mv(mv, a->final_norm);
             mv.ksplit = pick_ksplit(d.vocab_size, dim); mv.prefetch = a->opt_prefetch;
             pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(d.vocab_size, mv.ksplit, dim)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, mv);
         } else if (tc) {

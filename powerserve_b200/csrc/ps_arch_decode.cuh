@@ -25,7 +25,7 @@ __device__ __forceinline__ void pa_dot2(const bf16 *__restrict__ w0, const bf16 
                                         int k_begin = 0, int k_end = -1) {
     s0 = s1 = 0.f;
     if (k_end < 0) k_end = K;
-    if ((K & 7) == 0 && (k_begin & 7) == 0) {
+    if ((K & 7) == 0 && (k_begin & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) { // (a head's slice of x may start anywhere)
 #pragma unroll 4
         for (int k = k_begin + lane * 8; k < k_end; k += 256) {
             const uint4 a = __ldg(reinterpret_cast<const uint4 *>(w0 + k));
@@ -82,10 +82,47 @@ __device__ __forceinline__ void pa_norm_to_smem(float *hs, const float *__restri
     __syncthreads();
 }
 
+// block-wide seam of a sequential block (256 threads): hs = G(x + P(y); w_in) with P(y) = G(y; w_out) (w_out null: y itself; y null:
+// nothing joins), G over `groups` equal parts.  CTA 0 also stores the updated residual to x_out - a buffer other than x, which the
+// other CTAs are still reading.
+__device__ __forceinline__ void pa_seam_to_smem(float *hs, const float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w_out,
+                                                const float *__restrict__ w_in, float *__restrict__ x_out, int dim, int groups, float eps) {
+    __shared__ float red[8];
+    const int gs = dim / groups;
+    for (int g = 0; g < groups; g++) {
+        const int c0 = g * gs;
+        float inv = 1.0f;
+        if (y && w_out) {
+            float s = 0.f;
+            for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(y[c0 + c], y[c0 + c], s);
+            inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
+        }
+        float s2 = 0.f;
+        for (int c = threadIdx.x; c < gs; c += 256) {
+            float v = x[c0 + c];
+            if (y) v += w_out ? y[c0 + c] * inv * w_out[c0 + c] : y[c0 + c];
+            hs[c0 + c] = v;
+            if (x_out && blockIdx.x == 0 && blockIdx.y == 0) x_out[c0 + c] = v;
+            s2 = fmaf(v, v, s2);
+        }
+        if (w_in) {
+            const float inv2 = 1.0f / sqrtf(pa_block_sum(s2, red) / (float)gs + eps);
+            for (int c = threadIdx.x; c < gs; c += 256) hs[c0 + c] = hs[c0 + c] * inv2 * w_in[c0 + c]; // (a thread's own entries)
+        }
+    }
+    __syncthreads();
+}
+
 struct PaMv {
     const float *x;        // input vector [K]
     const float *norm_w;   // non-null: the input is normed first (K = model width)
     float eps;
+    // sequential blocks (groups > 0): the input is the seam G(x + P(seam_y; seam_w); norm_w); CTA 0 stores x + P(..) to x_out
+    int groups;
+    const float *seam_y, *seam_w;
+    float *x_out;
+    // per-head products (grp_rows > 0): rows [g * grp_rows, (g + 1) * grp_rows) read x + g * x_gs and write y + g * y_gs
+    int grp_rows, x_gs, y_gs;
     const bf16 *W;         // [N][K]
     const float *bias;     // [N] or null
     int N, K;
@@ -124,7 +161,10 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
     ps_grid_dep_launch();
     ps_grid_dep_wait();
     const float *xin = a.x;
-    if (a.norm_w) {
+    if (a.groups > 0) {
+        pa_seam_to_smem(pa_hs, a.x, a.seam_y, a.seam_w, a.norm_w, a.x_out, a.K, a.groups, a.eps);
+        xin = pa_hs;
+    } else if (a.norm_w) {
         pa_norm_to_smem(pa_hs, a.x, a.norm_w, a.K, a.eps);
         xin = pa_hs;
     }
@@ -135,7 +175,11 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
         float s0 = 0.f, s1 = 0.f;
         if (live) {
             const bf16 *w0 = row(n0), *w1 = row(n1);
-            if (n0 >= a.N) {
+            if (a.grp_rows > 0) { // every row reads its own head's slice of x
+                float t;
+                pa_dot2<ROUND>(w0, w0, xin + (n0 / a.grp_rows) * a.x_gs, a.K, 1.0f, lane, s0, t, k_begin, k_end);
+                pa_dot2<ROUND>(w1, w1, xin + (n1 / a.grp_rows) * a.x_gs, a.K, 1.0f, lane, s1, t, k_begin, k_end);
+            } else if (n0 >= a.N) {
                 pa_dot2<false>(w0, w1, xin, a.K, 1.0f, lane, s0, s1, k_begin, k_end);
             } else if (n1 >= a.N) { // the pair straddles the two matrices
                 float t;
@@ -166,6 +210,8 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
                     else a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
                 } else if (a.residual) {
                     a.residual[n] += v;
+                } else if (a.grp_rows > 0) {
+                    a.y[(n / a.grp_rows) * a.y_gs + n % a.grp_rows] = v;
                 } else {
                     a.y[n] = v;
                 }
@@ -192,7 +238,8 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t]; // a weight: fetched before the dependency wait
     ps_grid_dep_launch();
     ps_grid_dep_wait();
-    const int pos = pos_dev[0], j0 = blockIdx.x * PA_DS_KEYS;
+    const int pos = pos_dev[0], lo = pa_first_key(at, pos);
+    const int blk = lo / PA_DS_KEYS + blockIdx.x, j0 = blk * PA_DS_KEYS; // the grid starts at the block of the first key in sight
     if (j0 > pos) return;
     const int nj = min(PA_DS_KEYS, pos + 1 - j0);
     const bool bulk = (kd & 3) == 0;
@@ -209,7 +256,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     if (bulk && !ps_tc_wait(&bar, 0)) { if (tid == 0) err[0] = 5; return; }
     for (int t = tid; t < PA_DS_KEYS * H; t += 256) {
         const int jj = t % PA_DS_KEYS, h = t / PA_DS_KEYS;
-        if (jj >= nj) continue;
+        if (jj >= nj || j0 + jj < lo) continue;
         const float *kr = ks + jj * kds + (h / rep) * dq, *qr = qs + h * dq;
         float s;
         if ((dq & 3) == 0) {
@@ -231,7 +278,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     const int n_t = (PA_DS_KEYS * H + 31) & ~31;
     for (int t = tid; t < n_t; t += 256) {
         const int h = t / PA_DS_KEYS, jj = t % PA_DS_KEYS;
-        const bool valid = h < H && jj < nj;
+        const bool valid = h < H && jj < nj && j0 + jj >= lo;
         float s = -INFINITY;
         if (valid) {
             if (at.mix) {
@@ -248,9 +295,9 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
         float e = valid ? expf(s - m) : 0.f;
 #pragma unroll
         for (int o = PA_DS_KEYS / 2; o; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
-        if (valid && jj == 0) {
-            at.pm[(int64_t)h * at.ldP + blockIdx.x] = m;
-            at.pl[(int64_t)h * at.ldP + blockIdx.x] = e;
+        if (h < H && jj == 0) { // (every lane of the 16 holds the block's pair; the block has a key in sight)
+            at.pm[(int64_t)h * at.ldP + blk] = m;
+            at.pl[(int64_t)h * at.ldP + blk] = e;
         }
     }
 }
@@ -273,7 +320,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     ps_grid_dep_launch();
     ps_grid_dep_wait();
-    const int n = pos_dev[0] + 1;
+    const int n = pos_dev[0] + 1, lo = pa_first_key(at, n - 1);
     const bool bulk = (at.n_ctx & 3) == 0;
     if (bulk && tid == 0) {
         ps_mbar_init(&bar, 1);
@@ -284,16 +331,17 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     const int nb = (n + PA_DS_KEYS - 1) / PA_DS_KEYS;
     for (int r = warp; r < rep; r += 8) {
         const float *bm = at.pm + (int64_t)(g * rep + r) * at.ldP, *bl = at.pl + (int64_t)(g * rep + r) * at.ldP;
-        float mx = at.sink ? 0.f : -INFINITY;
-        for (int j = lane; j < nb; j += 32) mx = fmaxf(mx, bm[j]);
+        const float sk = pa_sink_logit(at, g * rep + r);
+        float mx = at.sink ? sk : -INFINITY;
+        for (int j = lo / PA_DS_KEYS + lane; j < nb; j += 32) mx = fmaxf(mx, bm[j]);
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.f;
-        for (int j = lane; j < nb; j += 32) sum = fmaf(bl[j], expf(bm[j] - mx), sum);
+        for (int j = lo / PA_DS_KEYS + lane; j < nb; j += 32) sum = fmaf(bl[j], expf(bm[j] - mx), sum);
 #pragma unroll
         for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if (lane == 0) {
-            if (at.sink) sum += expf(-mx);
+            if (at.sink) sum += expf(sk - mx);
             ms[r] = mx;
             inv[r] = 1.0f / sum;
         }
@@ -302,7 +350,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     const int dim_l = warp % PA_DP_DIMS, part = warp / PA_DP_DIMS, n_part = 8 / PA_DP_DIMS;
     const int c0 = blockIdx.x * PA_DP_DIMS;
     int it = 0;
-    for (int j0 = 0; j0 < n; j0 += chunk, it++) {
+    for (int j0 = lo & ~3; j0 < n; j0 += chunk, it++) { // (bulk copies start on 16-byte boundaries)
         const int nj = min(chunk, n - j0), nj4 = (nj + 3) & ~3;
         __syncthreads(); // the previous chunk's buffers are free
         if (bulk) {
@@ -320,7 +368,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
         }
         for (int t = tid; t < rep * nj4; t += 256) {
             const int r = t / nj4, jj = t % nj4;
-            ps[r * chunk + jj] = jj < nj ? expf(b[(int64_t)(g * rep + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
+            ps[r * chunk + jj] = (jj < nj && j0 + jj >= lo) ? expf(b[(int64_t)(g * rep + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
         }
         __syncthreads();
         if (bulk && !ps_tc_wait(&bar, it & 1)) { if (tid == 0) err[0] = 6; return; }
@@ -393,6 +441,29 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
         float gsum, usum;
         pa_dot2<ROUND>(wg, wu, pa_hs, dim, w, lane, gsum, usum);
         if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+    }
+}
+
+// dense gated feed-forward of a sequential block, first half: the seam in the prologue (the mixer's output joins the residual
+// stream, the result is normed), then y[n] = act(gate[n] . h, up[n] . h); a warp owns one ff row at a time, the CTAs walk the row
+// groups with the grid's stride
+template <bool ROUND>
+__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *__restrict__ x, const float *__restrict__ seam_y, const float *__restrict__ seam_w,
+                                                                   const float *__restrict__ norm_w, float *__restrict__ x_out, int groups, float eps, const bf16 *__restrict__ Wg,
+                                                                   const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, float limit, float alpha, float shift) {
+    extern __shared__ __align__(16) float pa_hs[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rows = PA_DV_ROWS / 2;
+    {
+        const int n = blockIdx.x * rows + warp;
+        if (n < ff) pa_prefetch2(Wg + (int64_t)n * dim, Wu + (int64_t)n * dim, 0, dim, lane);
+    }
+    ps_grid_dep_launch();
+    ps_grid_dep_wait();
+    pa_seam_to_smem(pa_hs, x, seam_y, seam_w, norm_w, x_out, dim, groups, eps);
+    for (int n = blockIdx.x * rows + warp; n < ff; n += gridDim.x * rows) {
+        float gsum, usum;
+        pa_dot2<ROUND>(Wg + (int64_t)n * dim, Wu + (int64_t)n * dim, pa_hs, dim, 1.0f, lane, gsum, usum);
+        if (lane == 0) y[n] = pa_expert_act(gsum, usum, limit, alpha, shift);
     }
 }
 
