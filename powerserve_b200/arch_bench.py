@@ -1,4 +1,11 @@
-"""bench.py --arch nufusun: prefill and decode throughput of the Nufusun design at layer sizes that resemble real models
+"""bench.py --arch nufusun | vanapel: prefill and decode throughput of a layer-list design at layer sizes that resemble real
+models (random weights), beside the closest existing model of the framework.
+
+--arch vanapel: the Vanapel design (windowed attention layers and one latent-attention layer, dense gated feed-forward) beside
+Nufusun at equal width, head geometry, layer count, vocabulary and as many ACTIVE feed-forward rows per token (top_k x expert
+ff = ff) - the same executor, kernels and bfloat16 weights, so the two steps move nearly the same bytes.
+
+--arch nufusun: prefill and decode throughput of the Nufusun design at layer sizes that resemble real models
 (random weights), beside the closest existing model of the framework - a llama stack (Q4_K) with the same width, head
 geometry, layer count, vocabulary and as many ACTIVE feed-forward rows per token (ffn = top_k x expert ff).
 
@@ -107,11 +114,95 @@ def run_size(name, prompt_len, steps, warmup, seed, chunk):
     return out
 
 
+# name: (width, heads, kv_heads, head size, window, ff, latent (heads, plain dims, rotated dims, value dims, q rank, kv rank), layer types, vocab)
+VANAPEL_SIZES = {
+    "s": (1024, 16, 4, 64, 512, 2048, (16, 64, 32, 64, 384, 256), "aala", 32000),
+    "m": (2048, 16, 4, 128, 1024, 5632, (16, 128, 64, 128, 768, 512), "aala", 32000),
+    "l": (4096, 32, 8, 128, 1024, 14336, (32, 128, 64, 128, 1536, 512), "al", 32000),
+}
+
+
+def _measure(m, prompt, chunk, steps, warmup):
+    for _ in range(2):
+        t_pre = _timed_prefill(m, prompt, chunk)
+    l0 = m.be.counter("kernel_launches")
+    t_dec = _timed_decode(m, prompt[-1], steps, warmup)
+    launches = m.be.counter("kernel_launches") - l0
+    t0 = time.perf_counter()
+    tok = prompt[-1]
+    for _ in range(16):
+        tok = int(np.argmax(m.forward([tok])[0]))
+    return t_pre, t_dec, launches / (steps + warmup), 16 / (time.perf_counter() - t0)
+
+
+def _load_synth(cfg, tensors, chunk, n_ctx):
+    d = tempfile.mkdtemp(prefix="ps_arch_")
+    try:
+        arch_synth.write_model_dir(d, cfg, tensors)
+        return arch.load_model(d, dtype="bfloat16", max_batch=chunk, n_ctx=n_ctx)
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
+
+
+def run_size_vanapel(name, prompt_len, steps, warmup, seed, chunk):
+    W, H, G, hs, win, ff, (LH, dn, dr, dv, rq, rk), kinds, V = VANAPEL_SIZES[name]
+    hbm, tflops, src = _peaks()
+    n_ctx = -(-(prompt_len + steps + warmup + 24) // 256) * 256
+    prompt = [int(v) for v in np.random.default_rng(1234).integers(0, V, prompt_len)]
+    out = {"size": name, "width": W, "heads": [H, G], "head_size": hs, "window": win, "ff": ff, "latent": [LH, dn, dr, dv, rq, rk], "layers": kinds, "vocab": V, "context": prompt_len}
+    layers = [arch_synth.vanapel_attention_layer(H, G, hs, hs, window=win, v_mix=True, ff=ff, limit=7.0) if k == "a" else
+              arch_synth.vanapel_latent_layer(LH, dn, dr, dv, rq, rk, rope_base=10000.0, scaling={"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}, ff=ff, limit=7.0)
+              for k in kinds]
+    cfg = arch_synth.vanapel_config(W, V, layers, groups=2)
+    m = _load_synth(cfg, arch_synth.vanapel_weights(cfg, seed=seed, fast=True), chunk, n_ctx)
+    t_pre, t_dec, launches, e2e = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    na, nlat = kinds.count("a"), kinds.count("l")
+    p_att = (H + 2 * G) * hs * W + H * hs * W
+    p_lat = (rq + rk + dr) * W + LH * (dn + dr) * rq + LH * dn * rk + LH * dv * rk + LH * dv * W
+    act_params = na * p_att + nlat * p_lat + len(kinds) * 3 * ff * W + V * W
+    keys_a = min(win, prompt_len)
+    kv_bytes = na * 2 * G * hs * 4 * keys_a + nlat * (2 * rk + dr) * 4 * prompt_len
+    # per token, averaged over the prompt: windowed layers see at most `win` keys, the latent layer (queries with W_uk folded in) all before it
+    attn_flops = na * 2 * 2 * H * hs * min(win, prompt_len / 2) + nlat * 2 * LH * (2 * rk + dr) * prompt_len / 2
+    out["vanapel"] = {
+        "prefill_tok_s": prompt_len / t_pre, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * act_params + attn_flops) * prompt_len / t_pre / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * act_params + attn_flops) * prompt_len / t_pre / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec, "decode_ms": t_dec * 1e3, "decode_launches_per_step": launches,
+        "decode_bytes_per_token": 2 * act_params + kv_bytes, "decode_frac_of_hbm_peak": (2 * act_params + kv_bytes) / t_dec / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e}
+
+    # ---- the closest existing model: Nufusun, 8 experts of ff / 2 rows, the best 2 active
+    nl, E, top, eff = len(kinds), 8, 2, ff // 2
+    ncfg = arch_synth.nufusun_config(W, V, [arch_synth.nufusun_layer(H, G, hs, hs, bias_max=float(prompt_len), experts=E, top=top, ff=eff, limit=7.0) for _ in range(nl)])
+    m = _load_synth(ncfg, arch_synth.nufusun_weights(ncfg, seed=seed, rel_rows=32, fast=True), chunk, n_ctx)
+    t_pre_n, t_dec_n, launches_n, e2e_n = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    n_params = nl * (p_att + E * W + top * 3 * eff * W) + V * W
+    n_kv = nl * 2 * G * hs * 4 * prompt_len
+    n_flops = nl * 2 * 2 * H * hs * prompt_len / 2
+    out["nufusun"] = {
+        "prefill_tok_s": prompt_len / t_pre_n, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * n_params + n_flops) * prompt_len / t_pre_n / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * n_params + n_flops) * prompt_len / t_pre_n / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec_n, "decode_ms": t_dec_n * 1e3, "decode_launches_per_step": launches_n,
+        "decode_bytes_per_token": 2 * n_params + n_kv, "decode_frac_of_hbm_peak": (2 * n_params + n_kv) / t_dec_n / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e_n}
+    out["peaks"] = {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}
+    return out
+
+
 def main(args) -> int:
     if capi.load_library().ps_cuda_device_count() == 0:
-        print(json.dumps({"arch": "nufusun", "unavailable": "no CUDA device: there is no CPU fallback"}))
+        print(json.dumps({"arch": args.arch, "unavailable": "no CUDA device: there is no CPU fallback"}))
         return 1
     sizes = [s for s in args.arch_sizes.split(",") if s]
+    if args.arch == "vanapel":
+        res = [run_size_vanapel(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
+        print(json.dumps({"arch": "vanapel", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",
+                          "sizes": res}))
+        return 0
     res = [run_size(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
     print(json.dumps({"arch": "nufusun", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",
                       "sizes": res}))

@@ -173,9 +173,12 @@ void build_bucket_table(int rows, float dmax, int n, std::vector<uint16_t> &t) {
 
 // shared memory of the single-token kernels
 size_t pa_dec_scores_smem(int H, int G, int dq) { return 4 * ((size_t)PA_DS_KEYS * (((G * dq + 3) & ~3) + 4) + (size_t)H * dq + (size_t)(PA_DS_KEYS + 1) * H + (size_t)H * H); }
-int pa_dec_pv_chunk(int H, int G) { return std::max(32, (PA_DP_FLOATS / (PA_DP_DIMS + H / G)) & ~31); }
+// the P.V kernel splits more than 4 query heads per kv head over blockIdx.z, 4 (or fewer) to a CTA
+int pa_dec_pv_split(int H, int G) { return (H / G + 3) / 4; }
+int pa_dec_pv_rep(int H, int G) { const int z = pa_dec_pv_split(H, G); return (H / G + z - 1) / z; }
+int pa_dec_pv_chunk(int H, int G) { return std::max(32, (PA_DP_FLOATS / (PA_DP_DIMS + pa_dec_pv_rep(H, G))) & ~31); }
 size_t pa_dec_pv_smem(int H, int G) {
-    const int rep = H / G;
+    const int rep = pa_dec_pv_rep(H, G);
     return 4 * ((size_t)(PA_DP_DIMS + rep) * pa_dec_pv_chunk(H, G) + (size_t)(2 + 8) * rep);
 }
 
@@ -611,7 +614,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         if (at.window > 0) blocks = std::min(blocks, cdiv(at.window, PA_DS_KEYS) + 1);
         pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
         PA_LAUNCH();
-        pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
+        pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G, pa_dec_pv_split(at.H, at.G)), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
                       pa_dec_pv_chunk(at.H, at.G), io.err_dev);
         PA_LAUNCH();
         return 0;
@@ -780,7 +783,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         if (single) {
             pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
             PA_LAUNCH();
-            pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
+            pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G, pa_dec_pv_split(H, G)), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();
         } else {
             pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs, 0);

@@ -311,7 +311,10 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
                                                    float *__restrict__ att, int chunk, int *__restrict__ err) {
     extern __shared__ __align__(16) float sm[];
     __shared__ __align__(8) uint64_t bar;
-    const int H = at.H, G = at.G, dv = at.dv, rep = H / G, g = blockIdx.y;
+    // blockIdx.z splits the query heads that share kv head g (many heads over one latent): this CTA takes `rep` of them from h0 on
+    const int H = at.H, G = at.G, dv = at.dv, rep_all = H / G, g = blockIdx.y;
+    const int rep_z = (rep_all + (int)gridDim.z - 1) / (int)gridDim.z, h0 = g * rep_all + (int)blockIdx.z * rep_z, rep = min(rep_z, rep_all - (int)blockIdx.z * rep_z);
+    if (rep <= 0) return;
     float *vs = sm;                         // [PA_DP_DIMS][chunk] V^T rows of the chunk
     float *ps = vs + PA_DP_DIMS * chunk;    // [rep][chunk] soft-max weights of the chunk (un-normalised)
     float *ms = ps + rep * chunk;           // [rep] row maxima
@@ -330,8 +333,8 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     // soft-max statistics of every head of the group from the scores kernel's per-block pairs: a warp per head
     const int nb = (n + PA_DS_KEYS - 1) / PA_DS_KEYS;
     for (int r = warp; r < rep; r += 8) {
-        const float *bm = at.pm + (int64_t)(g * rep + r) * at.ldP, *bl = at.pl + (int64_t)(g * rep + r) * at.ldP;
-        const float sk = pa_sink_logit(at, g * rep + r);
+        const float *bm = at.pm + (int64_t)(h0 + r) * at.ldP, *bl = at.pl + (int64_t)(h0 + r) * at.ldP;
+        const float sk = pa_sink_logit(at, h0 + r);
         float mx = at.sink ? sk : -INFINITY;
         for (int j = lo / PA_DS_KEYS + lane; j < nb; j += 32) mx = fmaxf(mx, bm[j]);
 #pragma unroll
@@ -368,7 +371,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
         }
         for (int t = tid; t < rep * nj4; t += 256) {
             const int r = t / nj4, jj = t % nj4;
-            ps[r * chunk + jj] = (jj < nj && j0 + jj >= lo) ? expf(b[(int64_t)(g * rep + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
+            ps[r * chunk + jj] = (jj < nj && j0 + jj >= lo) ? expf(b[(int64_t)(h0 + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
         }
         __syncthreads();
         if (bulk && !ps_tc_wait(&bar, it & 1)) { if (tid == 0) err[0] = 6; return; }
@@ -393,7 +396,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
         if (c0 + cc >= dv) continue;
         float s = 0.f;
         for (int pp = 0; pp < n_part; pp++) s += acc[(pp * PA_DP_DIMS + cc) * rep + r];
-        att[(g * rep + r) * dv + c0 + cc] = s * inv[r];
+        att[(h0 + r) * dv + c0 + cc] = s * inv[r];
     }
 }
 
