@@ -362,6 +362,7 @@ def test_long_decoding_past_every_window(tmp_path):
     ([LA(5, 6, 10, 3, 7, 33, scaling=YARN, ff=20), A(3, 3, 36, 4, window=2)], 48, 200, 4),          # odd ranks and sizes
     ([A(3, 1, 4, 36, window=90, v_mix=True, ff=72), LA(2, 16, 16, 16, 24, 24, rope_dims=8, scaling={"factor": 9.0, "original": 32, "fast": 4.0, "slow": 1.0})], 48, 200, 2),
     ([A(16, 4, 32, 32, window=48, v_mix=True, ff=96), A(16, 4, 32, 32, window=48, v_mix=True, ff=96)], 128, 300, 1),
+    ([A(5, 5, 6, 10, window=5, ff=37, limit=1.1), LA(3, 5, 6, 3, 7, 9, rope_dims=6, ff=13)], 50, 101, 5),                      # nothing a multiple of four
 ])
 def test_other_sizes(tmp_path, layers, width, vocab, groups):
     d, cfg, t = make(tmp_path, layers, width=width, vocab=vocab, seed=14, eps=1e-5, groups=groups)
