@@ -339,7 +339,7 @@ float ps_cuda_host_v_expf(float x);
  * from this function, so CPU-only tests can pin it */
 int ps_cuda_host_rel_bucket(int distance, int rows, float max_dist);
 /* host-side rotation frequencies of a layer-list attention (freq[dims / 2]; factor > 0: YaRN); returns the factor on
- * cos / sin.  The table the device reads is built from this function, so CPU-only tests can pin it */
+ * cos / sin.  The table the device reads holds the same values before their rounding to float32, so CPU-only tests can pin it */
 float ps_cuda_host_rope_freq(int dims, float base, float factor, int original, float fast, float slow, float *freq);
 
 #ifdef __cplusplus

@@ -40,7 +40,8 @@ struct PsArchLayer {
     int pw = 0;      // rows of the first projection (q|k|v, or q latent | kv latent | rotated key part)
     int aw = 0;      // width of the attention output rows (H * v_dim, or H * kv_rank before W_uv)
     bf16 *wuq = nullptr, *wukt = nullptr, *wuv = nullptr;
-    float *dq_norm = nullptr, *dkv_norm = nullptr, *rope_freq = nullptr;
+    float *dq_norm = nullptr, *dkv_norm = nullptr;
+    double *rope_freq = nullptr;
     float rope_mscale = 1.0f;
     uint8_t *t_uq = nullptr;
 };
@@ -208,9 +209,9 @@ extern "C" int ps_cuda_host_rel_bucket(int distance, int rows, float max_dist) {
     return (int)t[(size_t)distance];
 }
 
-// rotation frequencies of `dims` rotated dims, evaluated once on the host in double and rounded to float32: base^(-2 i / dims),
-// with factor > 0 blended towards f_i / factor along YaRN's ramp; returns the factor on cos / sin
-extern "C" float ps_cuda_host_rope_freq(int dims, float base, float factor, int original, float fast, float slow, float *freq) {
+// rotation frequencies of `dims` rotated dims, evaluated once on the host in double: base^(-2 i / dims), with factor > 0 blended
+// towards f_i / factor along YaRN's ramp; returns the factor on cos / sin
+static double rope_freq_host(int dims, float base, float factor, int original, float fast, float slow, double *freq) {
     const int half = dims / 2;
     double lo = 0, hi = 0, mscale = 1.0;
     if (factor > 0.f) {
@@ -225,9 +226,16 @@ extern "C" float ps_cuda_host_rope_freq(int dims, float base, float factor, int 
             const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
             fr = fr / factor * ramp + fr * (1.0 - ramp);
         }
-        freq[k] = (float)fr;
+        freq[k] = fr;
     }
-    return (float)mscale;
+    return mscale;
+}
+// the same table rounded to float32, for tests without a device
+extern "C" float ps_cuda_host_rope_freq(int dims, float base, float factor, int original, float fast, float slow, float *freq) {
+    std::vector<double> f((size_t)std::max(dims / 2, 1));
+    const double m = rope_freq_host(dims, base, factor, original, fast, slow, f.data());
+    for (int k = 0; k < dims / 2; k++) freq[k] = (float)f[(size_t)k];
+    return (float)m;
 }
 
 int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err) {
@@ -439,9 +447,10 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
             if ((rc = aalloc(a, (void **)&w.wukt, 2 * tr.size(), err))) return rc;
             PA_CK(cudaMemcpy(w.wukt, tr.data(), 2 * tr.size(), cudaMemcpyHostToDevice));
             if (l.rope_dims > 0) {
-                std::vector<float> f((size_t)l.rope_dims / 2);
-                w.rope_mscale = ps_cuda_host_rope_freq(l.rope_dims, l.rope_base, l.rope_factor, l.rope_original, l.rope_fast, l.rope_slow, f.data());
-                if ((rc = upload_f32(a, &w.rope_freq, f, err))) return rc;
+                std::vector<double> fd((size_t)l.rope_dims / 2);
+                w.rope_mscale = (float)rope_freq_host(l.rope_dims, l.rope_base, l.rope_factor, l.rope_original, l.rope_fast, l.rope_slow, fd.data());
+                if ((rc = aalloc(a, (void **)&w.rope_freq, fd.size() * 8, err))) return rc;
+                PA_CK(cudaMemcpy(w.rope_freq, fd.data(), fd.size() * 8, cudaMemcpyHostToDevice));
             }
         } else if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
                    (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
