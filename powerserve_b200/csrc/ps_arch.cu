@@ -2,8 +2,8 @@
 // kernels of the mechanisms a layer description can name.  The context (ps_cuda.cu) owns the stream, the cache sets and the
 // public entry points; this file owns what happens between the token ids and the logits.
 //
-// Precision contract.  The residual stream, norms, attention scores / soft-max weights, router logits and the K / V cache are
-// fp32 in BOTH compute modes.  PS_COMPUTE_BF16 rounds the ACTIVATION operand of every weight product to bfloat16 (weights are
+// Precision contract.  The residual stream, norms, rotation angles, attention scores / soft-max weights, router logits and the K / V
+// cache are fp32 in BOTH compute modes.  PS_COMPUTE_BF16 rounds the ACTIVATION operand of every weight product to bfloat16 (weights are
 // bfloat16 already) and accumulates in fp32; PS_COMPUTE_F32 feeds the fp32 activations unrounded and uses FMA chains only.
 #include "ps_arch.h"
 

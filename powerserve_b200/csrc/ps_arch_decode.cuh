@@ -1,13 +1,19 @@
-// ps_arch_decode.cuh - single-token (bs == 1) kernels of the layer-list executor: six launches per layer, every one
-// independent of the position except through device memory, so the step is captured once and replayed as a CUDA graph.
+// ps_arch_decode.cuh - single-token (bs == 1) kernels of the layer-list executor: six launches per parallel block (seven per
+// sequential block with windowed attention, eleven with latent attention), every one independent of the position except through
+// device memory, so the step is captured once and replayed as a CUDA graph.
 //
 //   pa_k_dec_mv          weight-streaming mat-vec (bfloat16 rows, 16-byte loads, two rows per warp) with fused prologue / epilogue:
 //                          norm of the residual stream in the prologue (q|k|v + router rows, lm_head),
 //                          bias, K row / V^T column straight into the cache, router logits from the UNROUNDED fp32 input,
-//                          residual add (output projection of a layer without a feed-forward)
-//   pa_k_dec_scores      scores of all heads for 16 keys per CTA (thread per key and head out of shared memory), distance bias, head
-//                        mixing, per-block soft-max statistics
-//   pa_k_dec_pv          soft-max statistics (+ sink) per head, weights staged once per CTA, P.V along contiguous V^T rows
+//                          residual add (output projection of a layer without a feed-forward);
+//                          sequential blocks: the seam in the prologue (the pending sublayer output joins the residual stream through
+//                          its group norm, the sum is group-normed for this product; CTA 0 stores the sum to the second residual buffer),
+//                          per-head products (a row reads its head's slice of the input)
+//   pa_k_dec_scores      scores of all heads for 16 keys per CTA (thread per key and head out of shared memory), distance bias (table or
+//                        logarithmic), head mixing, per-block soft-max statistics; with a window the grid starts at the first key in sight
+//   pa_k_dec_pv          soft-max statistics (+ sink logit) per head, weights staged once per CTA, P.V along contiguous V^T rows; many
+//                        heads over one kv head are split over blockIdx.z
+//   pa_k_dec_dense_up    seam in the prologue, gate | up rows of a dense feed-forward, activation
 //   pa_k_dec_expert_up   norm + top-k of the router scores in the prologue, gate | up rows of the chosen experts, activation
 //   pa_k_dec_expert_down down rows of the chosen experts summed over the slots + mixer output + residual
 #pragma once

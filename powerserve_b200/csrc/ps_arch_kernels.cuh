@@ -2,6 +2,8 @@
 //
 // Tiled kernels (any batch width): one 64 x 64 x 16 fp32 tile core shared by the dense projections, the routed experts
 // (rows gathered per expert), the attention scores (B operand = K cache rows) and P.V (B operand = V^T cache rows).
+// Sequential blocks add one-CTA-per-token kernels around them: the seam between two sublayers (group norm of the output, residual
+// add, group norm of the sum), unit-RMS q / k with the value blend on the way into the cache, the latent attention's norms and rotations.
 // The single-token kernels (bs == 1) live in ps_arch_decode.cuh.
 #pragma once
 
